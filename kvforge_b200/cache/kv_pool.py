@@ -1,6 +1,6 @@
 """Device storage of the cache: per group one K and one V tensor
 ``[entries, num_blocks, kv_heads, block_size, head_dim]`` (an entry per layer call that keeps
-a cache), and per stateful mixer call a float tensor ``[num_slots, *state_shape]``.
+a cache; V with the value size of a head where a mixer gives it one of its own), and per stateful mixer call a float tensor ``[num_slots, *state_shape]``.
 
 umarhassan-cloud/kvforge keeps ``[num_blocks, block_size, kv_heads, head_dim]`` per layer
 (src/tokenvault/cache/kv_cache.py:27-31).  Here the kv-head index comes before the
@@ -21,9 +21,9 @@ class KVPool:
         self.k: list[torch.Tensor] = []
         self.v: list[torch.Tensor] = []
         for g in model.groups:
-            shape = (len(g.calls), num_blocks, g.need.kv_heads, block_size, g.need.head_dim)
-            self.k.append(torch.zeros(shape, dtype=dtype, device=device))
-            self.v.append(torch.zeros(shape, dtype=dtype, device=device))
+            shape = (len(g.calls), num_blocks, g.need.kv_heads, block_size)
+            self.k.append(torch.zeros((*shape, g.need.head_dim), dtype=dtype, device=device))
+            self.v.append(torch.zeros((*shape, g.need.value_dim), dtype=dtype, device=device))
         self.states: list[torch.Tensor | None] = []
         for shape in model.state_shapes:
             self.states.append(None if shape is None else torch.zeros((num_slots, *shape), dtype=torch.float32, device=device))
@@ -57,4 +57,4 @@ def bytes_per_block(model, block_size: int, dtype: torch.dtype) -> int:
     """Bytes that one page index costs over all groups and entries, keys and values
     (src/tokenvault/config.py:91-95 for a single group)."""
     elem = torch.tensor([], dtype=dtype).element_size()
-    return sum(2 * len(g.calls) * block_size * g.need.kv_heads * g.need.head_dim * elem for g in model.groups)
+    return sum(len(g.calls) * block_size * g.need.kv_heads * (g.need.head_dim + g.need.value_dim) * elem for g in model.groups)

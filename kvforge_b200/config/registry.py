@@ -17,17 +17,20 @@ from .model_config import ConfigError, ModelConfig, RopeScaling
 @dataclass(frozen=True)
 class Architecture:
     name: str
-    parse_config: Callable[[dict[str, Any]], Any]  # config.json dict -> typed config
+    parse_config: Callable[..., Any]  # config.json dict (and tensor shapes, see below) -> typed config
     build_spec: Callable[[Any], Any]  # typed config -> parts.model.ModelSpec
+    # the file does not name every size: ``parse_config(config_json, tensor_shapes)`` also gets the
+    # checkpoint's tensor shapes (name -> shape)
+    needs_tensor_shapes: bool = False
 
 
 ARCHITECTURES: dict[str, Architecture] = {}
 
 
-def register_architecture(name: str, parse_config: Callable, build_spec: Callable) -> None:
+def register_architecture(name: str, parse_config: Callable, build_spec: Callable, needs_tensor_shapes: bool = False) -> None:
     if name in ARCHITECTURES:
         raise ValueError(f"architecture {name!r} is already registered")
-    ARCHITECTURES[name] = Architecture(name, parse_config, build_spec)
+    ARCHITECTURES[name] = Architecture(name, parse_config, build_spec, needs_tensor_shapes)
 
 
 def unregister_architecture(name: str) -> None:
@@ -42,9 +45,9 @@ def get_architecture(name: str) -> Architecture:
 
 
 def architecture_of(config_json: dict[str, Any]) -> Architecture:
-    archs = config_json.get("architectures")
+    archs = config_json.get("architectures") or ([config_json["architecture"]] if config_json.get("architecture") else None)
     if not archs:
-        raise ConfigError("config.json names no architecture (key 'architectures')")
+        raise ConfigError("config.json names no architecture (key 'architectures' or 'architecture')")
     return get_architecture(archs[0])
 
 
@@ -60,6 +63,11 @@ def _ensure_builtin() -> None:
 
     if "LlamaForCausalLM" not in ARCHITECTURES:
         register_architecture("LlamaForCausalLM", ModelConfig.from_hf_dict, llama_spec)
+    from ..models.mopilorn import mopilorn_spec
+    from .mopilorn_config import ARCHITECTURE, MopilornConfig
+
+    if ARCHITECTURE not in ARCHITECTURES:
+        register_architecture(ARCHITECTURE, MopilornConfig.from_dict, mopilorn_spec, needs_tensor_shapes=True)
 
 
 _LLAMA3_32 = RopeScaling(factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0, original_max_position_embeddings=8192)

@@ -14,7 +14,8 @@
 // leaves a row's state untouched.  So the result for a query does not depend on how the
 // prompt was cut, on the other rows of its tile, or on the physical pages.
 //
-// Cache layout per layer: K and V each [num_blocks][nkv][block_size][d].
+// Cache layout per layer: K [num_blocks][nkv][block_size][d] and V [num_blocks][nkv][block_size][dv]
+// (values may have a size of their own; the output rows then hold nh heads of dv).
 #include "common.cuh"
 
 using namespace kvf;
@@ -34,10 +35,10 @@ struct AttnParams {
   const int* block_tables;
   const int* qsl;
   const int* ctx_lens;
-  float* part_acc;  // split mode: [B][nh][splits][d]
+  float* part_acc;  // split mode: [B][nh][splits][dv]
   float* part_ml;   // split mode: [B][nh][splits][2]
   int q_stride, out_stride, bt_stride;
-  int nh, nkv, d, block_size;
+  int nh, nkv, d, dv, block_size;
   int gh, chunks, tq;  // heads per CTA, head chunks per kv head, tokens per CTA
   int window;
   int split_size, max_splits;
@@ -67,9 +68,10 @@ template <typename T, int DPL, bool SPLIT>
 __global__ void __launch_bounds__(WARPS * 32) paged_attn_generic_kernel(const AttnParams p) {
   extern __shared__ __align__(16) float smem[];
   const int d = p.d, ldk = d + 4;
+  const int dv = p.dv, ldv = dv + 4;
   float* Ks = smem;                    // [TK][ldk]
-  float* Vs = Ks + TK * ldk;           // [TK][ldk]
-  float* Qs = Vs + TK * ldk;           // [ROWS][d]
+  float* Vs = Ks + TK * ldk;           // [TK][ldv]
+  float* Qs = Vs + TK * ldv;           // [ROWS][d]
   float* Ps = Qs + ROWS * d;           // [WARPS][RPW][TK]
 
   const int b = blockIdx.y;
@@ -140,30 +142,30 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attn_generic_kernel(const At
   const T* vc = (const T*)p.vcache;
   const int* bt = p.block_tables + (size_t)b * p.bt_stride;
   constexpr int VN = Vec<T>::N;
-  const int vec_per_row = d / VN;
+  const int vec_per_row = d / VN, vvec_per_row = dv / VN;
 
   for (int t0 = kv_lo; t0 < kv_hi; t0 += TK) {
     __syncthreads();  // previous tile consumed (and Qs staged, first time)
     // ---- load the K and V tile as float; keys >= ctx and released pages are zero-filled
-    for (int idx = threadIdx.x; idx < TK * vec_per_row; idx += blockDim.x) {
-      const int key = idx / vec_per_row, c = (idx - key * vec_per_row) * VN;
+    for (int idx = threadIdx.x; idx < TK * (vec_per_row + vvec_per_row); idx += blockDim.x) {
+      const bool is_v = idx >= TK * vec_per_row;
+      const int i2 = is_v ? idx - TK * vec_per_row : idx;
+      const int per = is_v ? vvec_per_row : vec_per_row, width = is_v ? dv : d;
+      const int key = i2 / per, c = (i2 - key * per) * VN;
       const int kp = t0 + key;
-      float kf[VN], vf[VN];
+      float f[VN];
       const int blk = kp < ctx ? bt[kp / p.block_size] : -1;
       if (blk >= 0) {  // a page given back (-1) lies wholly outside every window: zeros
         const int off = kp % p.block_size;
-        const size_t base = (((size_t)blk * p.nkv + kvh) * p.block_size + off) * d + c;
-        load_vec_to_float<T>(kc + base, kf);
-        load_vec_to_float<T>(vc + base, vf);
+        const size_t base = (((size_t)blk * p.nkv + kvh) * p.block_size + off) * width + c;
+        load_vec_to_float<T>((is_v ? vc : kc) + base, f);
       } else {
 #pragma unroll
-        for (int e = 0; e < VN; ++e) kf[e] = vf[e] = 0.f;
+        for (int e = 0; e < VN; ++e) f[e] = 0.f;
       }
+      float* dst = is_v ? Vs + key * ldv + c : Ks + key * ldk + c;
 #pragma unroll
-      for (int e = 0; e < VN; ++e) {
-        Ks[key * ldk + c + e] = kf[e];
-        Vs[key * ldk + c + e] = vf[e];
-      }
+      for (int e = 0; e < VN; ++e) dst[e] = f[e];
     }
     __syncthreads();
 
@@ -214,7 +216,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attn_generic_kernel(const At
 #pragma unroll
         for (int e = 0; e < DPL; ++e) {
           const int dim = lane + 32 * e;
-          const float v = (dim < d) ? Vs[(j + jj) * ldk + dim] : 0.f;
+          const float v = (dim < dv) ? Vs[(j + jj) * ldv + dim] : 0.f;
 #pragma unroll
           for (int i = 0; i < RPW; ++i) {
             const float pv = jj == 0 ? p4[i].x : jj == 1 ? p4[i].y : jj == 2 ? p4[i].z : p4[i].w;
@@ -241,15 +243,15 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attn_generic_kernel(const At
 #pragma unroll
       for (int e = 0; e < DPL; ++e) {
         const int dim = lane + 32 * e;
-        if (dim < d) p.part_acc[slot * d + dim] = acc[i][e];
+        if (dim < dv) p.part_acc[slot * dv + dim] = acc[i][e];
       }
     } else {
       const float inv = l[i] > 0.f ? 1.f / l[i] : 0.f;
-      T* o = (T*)p.out + (size_t)(q_begin + q0 + tok) * p.out_stride + (size_t)head * d;
+      T* o = (T*)p.out + (size_t)(q_begin + q0 + tok) * p.out_stride + (size_t)head * dv;
 #pragma unroll
       for (int e = 0; e < DPL; ++e) {
         const int dim = lane + 32 * e;
-        if (dim < d) o[dim] = from_float<T>(acc[i][e] * inv);
+        if (dim < dv) o[dim] = from_float<T>(acc[i][e] * inv);
       }
     }
   }
@@ -288,7 +290,7 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_acc, const fl
 
 template <typename T, int DPL, bool SPLIT>
 int launch_generic(const AttnParams& p, dim3 grid, cudaStream_t st) {
-  const size_t smem = (size_t)(2 * TK * (p.d + 4) + ROWS * p.d + WARPS * RPW * TK) * sizeof(float);
+  const size_t smem = (size_t)(TK * (p.d + 4) + TK * (p.dv + 4) + ROWS * p.d + WARPS * RPW * TK) * sizeof(float);
   auto kern = paged_attn_generic_kernel<T, DPL, SPLIT>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -300,9 +302,9 @@ int launch_generic(const AttnParams& p, dim3 grid, cudaStream_t st) {
 
 template <typename T, bool SPLIT>
 int dispatch_dpl(const AttnParams& p, dim3 grid, cudaStream_t st) {
-  if (p.d <= 32) return launch_generic<T, 1, SPLIT>(p, grid, st);
-  if (p.d <= 64) return launch_generic<T, 2, SPLIT>(p, grid, st);
-  if (p.d <= 128) return launch_generic<T, 4, SPLIT>(p, grid, st);
+  if (p.dv <= 32) return launch_generic<T, 1, SPLIT>(p, grid, st);
+  if (p.dv <= 64) return launch_generic<T, 2, SPLIT>(p, grid, st);
+  if (p.dv <= 128) return launch_generic<T, 4, SPLIT>(p, grid, st);
   return launch_generic<T, 8, SPLIT>(p, grid, st);
 }
 
@@ -310,17 +312,18 @@ template <typename T>
 int paged_attention_generic(const void* q, void* out, const void* kcache, const void* vcache,
                             const int* block_tables, const int* qsl, const int* ctx_lens, int B,
                             int max_q_len, int q_stride, int out_stride, int bt_stride, int nh, int nkv,
-                            int d, int block_size, float scale, int window, int split_size, int max_splits,
+                            int d, int dv, int block_size, float scale, int window, int split_size, int max_splits,
                             int grid_splits, float* part_acc, float* part_ml, cudaStream_t st) {
   if (B <= 0 || max_q_len <= 0) return 0;
-  if (d <= 0 || d > 256 || (d % 8) != 0 || nkv <= 0 || nh % nkv != 0 || block_size <= 0)
+  if (dv <= 0) dv = d;
+  if (d <= 0 || d > 256 || (d % 8) != 0 || dv > 256 || (dv % 8) != 0 || nkv <= 0 || nh % nkv != 0 || block_size <= 0)
     return (int)cudaErrorInvalidValue;
   AttnParams p;
   p.q = q; p.out = out; p.kcache = kcache; p.vcache = vcache;
   p.block_tables = block_tables; p.qsl = qsl; p.ctx_lens = ctx_lens;
   p.part_acc = part_acc; p.part_ml = part_ml;
   p.q_stride = q_stride; p.out_stride = out_stride; p.bt_stride = bt_stride;
-  p.nh = nh; p.nkv = nkv; p.d = d; p.block_size = block_size;
+  p.nh = nh; p.nkv = nkv; p.d = d; p.dv = dv; p.block_size = block_size;
   const int g = nh / nkv;
   p.gh = g < ROWS ? g : ROWS;
   p.chunks = (g + p.gh - 1) / p.gh;
@@ -336,7 +339,7 @@ int paged_attention_generic(const void* q, void* out, const void* kcache, const 
     dim3 grid(grid_splits > 0 && grid_splits < max_splits ? grid_splits : max_splits, B, nkv * p.chunks);
     int rc = dispatch_dpl<T, true>(p, grid, st);
     if (rc) return rc;
-    attn_combine_kernel<T><<<dim3(nh, B), 64, 0, st>>>(part_acc, part_ml, (T*)out, qsl, ctx_lens, nh, d,
+    attn_combine_kernel<T><<<dim3(nh, B), 64, 0, st>>>(part_acc, part_ml, (T*)out, qsl, ctx_lens, nh, dv,
                                                        out_stride, split_size, max_splits);
     return KVF_LAUNCH_STATUS();
   }
@@ -350,10 +353,10 @@ int paged_attention_generic(const void* q, void* out, const void* kcache, const 
   KVF_API int kvf_paged_attention_generic_##SUF(                                                          \
       const void* q, void* out, const void* kcache, const void* vcache, const int* block_tables,          \
       const int* qsl, const int* ctx_lens, int B, int max_q_len, int q_stride, int out_stride,            \
-      int bt_stride, int nh, int nkv, int d, int block_size, float scale, int window, int split_size,     \
-      int max_splits, int grid_splits, float* part_acc, float* part_ml, cudaStream_t st) {                \
+      int bt_stride, int nh, int nkv, int d, int dv, int block_size, float scale, int window,             \
+      int split_size, int max_splits, int grid_splits, float* part_acc, float* part_ml, cudaStream_t st) { \
     return paged_attention_generic<T>(q, out, kcache, vcache, block_tables, qsl, ctx_lens, B, max_q_len,  \
-                                      q_stride, out_stride, bt_stride, nh, nkv, d, block_size, scale,     \
+                                      q_stride, out_stride, bt_stride, nh, nkv, d, dv, block_size, scale, \
                                       window, split_size, max_splits, grid_splits, part_acc, part_ml,     \
                                       st);                                                                \
   }

@@ -22,6 +22,7 @@ from ..config.registry import architecture_of, get_architecture
 from ..parts.model import DecoderModel, ModelSpec
 from ..weights.loader import load_weights
 from ..weights.random_init import random_weights
+from ..weights.safetensors_io import open_model_files
 from .runtime import Runtime
 from .step import ModelRunner
 
@@ -30,7 +31,14 @@ def spec_from_model_dir(model_dir: str | Path):
     """(typed config, ModelSpec) of a model folder; the class is chosen by ``config.json``."""
     cj = read_config_json(model_dir)
     arch = architecture_of(cj)
-    cfg = arch.parse_config(cj)
+    if arch.needs_tensor_shapes:
+        shapes = {}
+        for f in open_model_files(model_dir):
+            shapes.update({name: tuple(f.info(name)[1]) for name in f.keys()})
+            f.close()
+        cfg = arch.parse_config(cj, shapes)
+    else:
+        cfg = arch.parse_config(cj)
     return cfg, arch.build_spec(cfg)
 
 

@@ -36,6 +36,9 @@ LIBRARIES: dict[str, tuple[list[str], list[str]]] = {
     # one entry point that allocates nothing (csrc/kvforge_noalloc.h); a library of its own, so
     # that only a process that asks for it holds its built-in scratch array
     "noalloc": (["attention_decode_noalloc.cu"], []),
+    # what mixers with a running state, several residual streams and the general rotary form need; a
+    # library of its own, so that a model without them never compiles it
+    "mixers": (["sequence_mix.cu", "streams.cu"], []),
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

@@ -24,7 +24,7 @@ _SIGNATURES = {
     "kvf_rope_cache_{s}": "ppilppppppiiiiiilpp",
     "kvf_silu_mul_{s}": "ppliip",
     "kvf_cast_from_float_{s}": "pplp",
-    "kvf_paged_attention_generic_{s}": "pppppppiiiiiiiiifiiiippp",
+    "kvf_paged_attention_generic_{s}": "pppppppiiiiiiiiiifiiiippp",
     "kvf_paged_attention_mma_bf16": "pppppppiiiiiiiiifiiiippp",
     "kvf_paged_attention_tcgen05_bf16": "pppppppiiiiiiiiilfipipp",
     "kvf_paged_attention_decode_fused_bf16": "pppppppiiiiiiiifiiiipppp",
@@ -35,6 +35,15 @@ _SIGNATURES = {
     "kvf_gemm_tcgen05_bf16": "pppiiiiiiipp",
     "kvf_sample_f32": "pliippppppp",
     "kvf_argmax_f32": "pliipipp",
+    # library "mixers"
+    "kvf_causal_conv_{s}": "pipplppiiiiipip",
+    "kvf_gated_delta_{s}": "pppipipippiplpippiiiiiffp",
+    "kvf_gated_head_norm_{s}": "pipipfiliipip",
+    "kvf_hc_step_{s}": "pppilppppppiiifp",
+    "kvf_branch_norm_mean_{s}": "pppppilifpp",
+    "kvf_rope_cache_general_{s}": "pipppppiiiiiiiilpp",
+    "kvf_replicate_streams": "ppliip",
+    "kvf_softcap_f32": "plfp",
 }
 _CTYPES = {"p": ctypes.c_void_p, "i": ctypes.c_int, "l": ctypes.c_longlong, "f": ctypes.c_float}
 
@@ -467,9 +476,14 @@ def paged_attention(
     query_tiles: tuple[torch.Tensor, int] | None = None,
     single_only: bool = False,
     wave_target: int = 0,
+    dv: int | None = None,
 ) -> None:
     """Paged GQA attention of a flat batch (the contract is at the top of
     ``csrc/attention_generic.cu``).
+
+    ``dv``: size of a value head when it differs from ``d`` (``vcache`` is then
+    ``[num_blocks, nkv, block_size, dv]`` and ``out`` ``[N, nh*dv]``); only the FP32-pipe kernel
+    takes such a shape.
 
     ``q``: rows of ``q_stride`` elements whose first ``nh*d`` are the query heads; ``out``:
     ``[N, nh*d]``.  With ``scratch`` (and every sequence holding one query) the decode form
@@ -496,8 +510,14 @@ def paged_attention(
     _need(block_tables, torch.int32, "block_tables")
     _need(qsl, torch.int32, "query_start_loc")
     _need(ctx_lens, torch.int32, "context_lens")
-    if kcache.dim() != 4 or kcache.shape[1] != nkv or kcache.shape[3] != d or kcache.shape != vcache.shape:
-        raise ValueError("paged_attention: cache shape must be [num_blocks, nkv, block_size, d]")
+    dv = d if dv is None else int(dv)
+    check_head_dim(dv)
+    if kcache.dim() != 4 or kcache.shape[1] != nkv or kcache.shape[3] != d or tuple(vcache.shape) != (*kcache.shape[:3], dv):
+        raise ValueError("paged_attention: cache shapes must be [num_blocks, nkv, block_size, d] and [..., dv]")
+    if dv != d:
+        if kernel not in ("auto", "generic"):
+            raise ValueError("only the FP32-pipe attention kernel takes a value size of its own")
+        kernel = "generic"
     block_size = kcache.shape[2]
     if q_stride is None:
         q_stride = q.shape[-1]
@@ -518,7 +538,7 @@ def paged_attention(
             raise ValueError("split_size must be a positive multiple of 64")
         split = split_size
         max_splits = pa.shape[2]
-        if pa.shape[0] < num_seqs or pa.shape[1] != nh or pa.shape[3] != d:
+        if pa.shape[0] < num_seqs or pa.shape[1] != nh or pa.shape[3] != dv:
             raise ValueError("paged_attention: scratch shape does not fit")
         if max_context is None or -(-max_context // split) > max_splits:
             raise ValueError("paged_attention: scratch is too small for the longest context")
@@ -586,7 +606,7 @@ def paged_attention(
     _check(
         _fn(name)(
             _ptr(q), _ptr(out), _ptr(kcache), _ptr(vcache), _ptr(block_tables), _ptr(qsl), _ptr(ctx_lens),
-            num_seqs, max_q_len, q_stride, out.shape[-1], bt_stride, nh, nkv, d, block_size, float(scale),
+            num_seqs, max_q_len, q_stride, out.shape[-1], bt_stride, nh, nkv, d, *((dv,) if not use_mma else ()), block_size, float(scale),
             int(window), split, max_splits, grid_splits, _ptr(pa), _ptr(pm), _stream(),
         ),
         name,
@@ -883,3 +903,289 @@ def splitmix64(z: int) -> int:
     z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & m
     z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & m
     return z ^ (z >> 31)
+
+
+# ------------------------------------------------------------------ mixers with a running state (library "mixers")
+
+MIXERS_LIB = "mixers"
+
+
+def _rows2d(t: torch.Tensor, dtype: torch.dtype | None, what: str) -> None:
+    """A 2-D tensor (or a column slice of one): unit inner stride, any row stride."""
+    _need(t, dtype, what, contiguous=False)
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise ValueError(f"{what} must be 2-D with unit inner stride")
+
+
+def _state_view(state: torch.Tensor, width: int, what: str) -> tuple[int, int]:
+    """Pointer to slot 0's part and the stride between slots of a float state ``[slots, width]``
+    (a column slice of the pool's rows)."""
+    _need(state, torch.float32, what, contiguous=False)
+    if state.dim() != 2 or state.shape[1] != width or state.stride(1) != 1:
+        raise ValueError(f"{what} must be float [slots, {width}] with unit inner stride")
+    return state.data_ptr(), state.stride(0)
+
+
+def causal_conv(
+    x: torch.Tensor, weight: torch.Tensor, state: torch.Tensor, qsl: torch.Tensor, state_slots: torch.Tensor,
+    num_seqs: int, out: torch.Tensor, activation: str | None = None,
+) -> None:  # fmt: skip
+    """Short causal convolution over time per channel of a flat batch, and the state moved on.
+
+    ``x [N, C]`` (rows may be a slice of a wider buffer), ``weight`` float ``[C, taps]`` whose last
+    column multiplies the current token, ``state`` float ``[slots, (taps-1)*C]``: the last
+    ``taps-1`` inputs of each sequence, oldest first, zeros before its start.  ``out [N, C]`` gets
+    the sums (``activation``: ``None`` or ``"silu"``); afterwards the state holds this step's last
+    inputs.  Sequences without rows and slots below zero are left alone."""
+    s = _suffix(x.dtype)
+    _rows2d(x, None, "x")
+    _rows2d(out, x.dtype, "out")
+    _need(weight, torch.float32, "conv weight")
+    n, c = x.shape
+    taps = weight.shape[1]
+    if tuple(weight.shape) != (c, taps) or tuple(out.shape) != (n, c):
+        raise ValueError("causal_conv: shapes do not agree")
+    if activation not in (None, "silu"):
+        raise ValueError("causal_conv: activation must be None or 'silu'")
+    sptr, sstride = (0, 0) if taps == 1 else _state_view(state, (taps - 1) * c, "conv state")
+    _need(qsl, torch.int32, "query_start_loc")
+    _need(state_slots, torch.int32, "state_slots")
+    name = f"kvf_causal_conv_{s}"
+    _check(
+        _fn(name, MIXERS_LIB)(
+            _ptr(x), x.stride(0), _ptr(weight), sptr, sstride, _ptr(qsl), _ptr(state_slots), n, num_seqs, c, taps,
+            1 if activation == "silu" else 0, _ptr(out), out.stride(0), _stream(),
+        ),
+        name,
+        1 if taps == 1 else 2,
+    )  # fmt: skip
+
+
+def gated_delta(
+    q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta_logits: torch.Tensor, step_logits: torch.Tensor,
+    a_log: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor, out: torch.Tensor, qsl: torch.Tensor,
+    state_slots: torch.Tensor, num_seqs: int, num_heads: int, num_kv_heads: int, dk: int, dv: int, q_scale: float,
+    norm_eps: float = 1e-6,
+) -> None:  # fmt: skip
+    """The gated delta rule over a flat batch, token by token per sequence, on the state
+    ``S [heads, dk, dv]`` of each sequence's slot (``csrc/sequence_mix.cu`` has the equations).
+
+    ``q, k [N, G*dk]`` and ``v [N, H*dv]`` are column slices of one buffer (same row stride);
+    ``beta_logits`` float ``[N, H]``; ``step_logits`` float ``[N, H]`` (one decay a head) or
+    ``[N, H*dk]`` (one a key channel), with ``dt_bias`` of the same width and ``a_log [H]``;
+    ``out`` float ``[N, H*dv]`` gets the read-out."""
+    s = _suffix(q.dtype)
+    h, g = int(num_heads), int(num_kv_heads)
+    for t, w, what in ((q, g * dk, "q"), (k, g * dk, "k"), (v, h * dv, "v")):
+        _rows2d(t, q.dtype, what)
+        if t.shape[1] != w or t.shape[0] != q.shape[0] or t.stride(0) != q.stride(0):
+            raise ValueError(f"gated_delta: {what} must be [N, {w}] with the row stride of q")
+    n = q.shape[0]
+    _rows2d(beta_logits, torch.float32, "beta_logits")
+    _rows2d(step_logits, torch.float32, "step_logits")
+    _rows2d(out, torch.float32, "out")
+    per_channel = step_logits.shape[1] != h
+    if beta_logits.shape != (n, h) or step_logits.shape[1] not in (h, h * dk) or step_logits.shape[0] != n or tuple(out.shape) != (n, h * dv):
+        raise ValueError("gated_delta: shapes do not agree")
+    _need(a_log, torch.float32, "A_log")
+    _need(dt_bias, torch.float32, "dt_bias")
+    if a_log.numel() != h or dt_bias.numel() != step_logits.shape[1]:
+        raise ValueError("gated_delta: A_log must be [H] and dt_bias as wide as the step logits")
+    sptr, sstride = _state_view(state, h * dk * dv, "delta state")
+    _need(qsl, torch.int32, "query_start_loc")
+    _need(state_slots, torch.int32, "state_slots")
+    name = f"kvf_gated_delta_{s}"
+    _check(
+        _fn(name, MIXERS_LIB)(
+            _ptr(q), _ptr(k), _ptr(v), q.stride(0), _ptr(beta_logits), beta_logits.stride(0), _ptr(step_logits),
+            step_logits.stride(0), _ptr(a_log), _ptr(dt_bias), 1 if per_channel else 0, sptr, sstride, _ptr(out),
+            out.stride(0), _ptr(qsl), _ptr(state_slots), num_seqs, h, g, dk, dv, float(q_scale), float(norm_eps), _stream(),
+        ),
+        name,
+    )  # fmt: skip
+
+
+def gated_head_norm(
+    o: torch.Tensor, gate: torch.Tensor | None, weight: torch.Tensor, eps: float, out: torch.Tensor, num_heads: int, dv: int,
+    activation: str | None = "silu",
+) -> None:  # fmt: skip
+    """``out[n, h, :] = o / sqrt(mean(o^2) + eps) * weight * act(gate)`` per token and head; ``o``
+    float ``[N, H*dv]``, ``gate`` and ``out`` in the storage type, ``activation``: ``"silu"``,
+    ``"sigmoid"`` or ``None`` (no gate)."""
+    s = _suffix(out.dtype)
+    _rows2d(o, torch.float32, "o")
+    _rows2d(out, None, "out")
+    _need(weight, torch.float32, "head norm weight")
+    n = o.shape[0]
+    if o.shape[1] != num_heads * dv or tuple(out.shape) != (n, num_heads * dv) or weight.numel() != dv:
+        raise ValueError("gated_head_norm: shapes do not agree")
+    act = {None: 0, "silu": 1, "sigmoid": 2}.get(activation, -1)
+    if act < 0:
+        raise ValueError("gated_head_norm: activation must be 'silu', 'sigmoid' or None")
+    gptr, gstride = None, 0
+    if act:
+        _rows2d(gate, out.dtype, "gate")
+        if tuple(gate.shape) != (n, num_heads * dv):
+            raise ValueError("gated_head_norm: gate shape")
+        gptr, gstride = _ptr(gate), gate.stride(0)
+    name = f"kvf_gated_head_norm_{s}"
+    _check(
+        _fn(name, MIXERS_LIB)(_ptr(o), o.stride(0), gptr, gstride, _ptr(weight), float(eps), act, n, num_heads, dv, _ptr(out), out.stride(0), _stream()),
+        name,
+    )
+
+
+# ------------------------------------------------------------------ several residual streams (library "mixers")
+
+MAX_STREAMS = 16
+MAX_BRANCHES = 4
+
+
+@dataclass
+class StreamWrite:
+    """What a sublayer of a block with several residual streams leaves for the next read: its
+    result ``y`` (a tensor in the storage type or ``Partials``), and how it enters the streams:
+    ``x_t <- sum_s mix[s, t] x_s + out[t] y``."""
+
+    y: torch.Tensor | Partials
+    mix: torch.Tensor  # float [S, S], (from, to)
+    out: torch.Tensor  # float [S]
+
+
+def stream_step(
+    streams: torch.Tensor, pending: StreamWrite | None, read: torch.Tensor | None, norm_weight: torch.Tensor, out: torch.Tensor,
+    eps: float, num_streams: int, rows: torch.Tensor | None = None,
+) -> None:  # fmt: skip
+    """One kernel between two sublayers of a model with ``S`` residual streams ``[N, S*W]`` (float):
+    the pending write moves the streams on, then ``u = sum_t read[t] x_t`` (``read=None``: the plain
+    sum of the streams) is normed: ``out = T(u * rsqrt(mean(u^2) + eps) * norm_weight)``.  With
+    ``rows`` (int32) out row ``r`` comes from token ``rows[r]`` and the streams are not written."""
+    s = _suffix(out.dtype)
+    _need(streams, torch.float32, "streams")
+    _need(out, None, "out")
+    _need(norm_weight, torch.float32, "norm weight")
+    w = out.shape[-1]
+    n_rows = out.shape[0]
+    if streams.shape[-1] != num_streams * w or norm_weight.numel() != w or not 0 < num_streams <= MAX_STREAMS:
+        raise ValueError("stream_step: shapes do not agree")
+    yptr, pptr, nsplit, stride, mix, ow = None, None, 0, 0, None, None
+    if pending is not None:
+        y = pending.y
+        if isinstance(y, Partials):
+            _need(y.t, torch.float32, "partials", contiguous=False)
+            if y.t.shape[-1] != w or y.t.stride(1) != w or y.t.stride(2) != 1:
+                raise ValueError("stream_step: partials must be [S, N, W] with dense rows")
+            pptr, nsplit, stride = _ptr(y.t), y.nsplit, y.split_stride
+        else:
+            _need(y, out.dtype, "pending result")
+            if y.shape[-1] != w:
+                raise ValueError("stream_step: pending result width")
+            yptr = _ptr(y)
+        _need(pending.mix, torch.float32, "mix")
+        _need(pending.out, torch.float32, "out weights")
+        if pending.mix.numel() != num_streams * num_streams or pending.out.numel() != num_streams:
+            raise ValueError("stream_step: mix must be [S, S] and out [S]")
+        mix, ow = pending.mix, pending.out
+    if read is not None:
+        _need(read, torch.float32, "read weights")
+        if read.numel() != num_streams:
+            raise ValueError("stream_step: read must be [S]")
+    if rows is not None:
+        _need(rows, torch.int32, "rows")
+        if rows.numel() < n_rows:
+            raise ValueError("stream_step: fewer row indices than output rows")
+    elif streams.shape[0] < n_rows:
+        raise ValueError("stream_step: fewer stream rows than output rows")
+    name = f"kvf_hc_step_{s}"
+    _check(
+        _fn(name, MIXERS_LIB)(
+            _ptr(streams), yptr, pptr, nsplit, stride, _ptr(mix), _ptr(ow), _ptr(read), _ptr(norm_weight), _ptr(out), _ptr(rows),
+            n_rows, num_streams, w, float(eps), _stream(),
+        ),
+        name,
+    )  # fmt: skip
+
+
+def replicate_streams(src: torch.Tensor, streams: torch.Tensor, num_streams: int) -> None:
+    """``streams[n, s, :] = src[n, :]`` for every stream (float)."""
+    _need(src, torch.float32, "src")
+    _need(streams, torch.float32, "streams")
+    n, w = src.shape
+    if tuple(streams.shape) != (n, num_streams * w):
+        raise ValueError("replicate_streams: shapes do not agree")
+    name = "kvf_replicate_streams"
+    _check(_fn(name, MIXERS_LIB)(_ptr(src), _ptr(streams), n, num_streams, w, _stream()), name)
+
+
+def branch_norm_mean(results: list, weights: list[torch.Tensor], eps: float, out: torch.Tensor) -> None:
+    """``out = T(mean_b rmsnorm(results[b]) * weights[b])`` over the model width: the results of
+    mixers that ran side by side on the same input (tensors in the storage type or ``Partials``)."""
+    s = _suffix(out.dtype)
+    _need(out, None, "out")
+    n, w = out.shape
+    nb = len(results)
+    if not 0 < nb <= MAX_BRANCHES or len(weights) != nb:
+        raise ValueError(f"branch_norm_mean: between 1 and {MAX_BRANCHES} branches, a weight each")
+    P, L, I = ctypes.c_void_p * nb, ctypes.c_longlong * nb, ctypes.c_int * nb
+    ys, ps, ns, ss, ws = P(), P(), I(), L(), P()
+    for b, (y, wt) in enumerate(zip(results, weights)):
+        _need(wt, torch.float32, "branch norm weight")
+        if wt.numel() != w:
+            raise ValueError("branch_norm_mean: weight width")
+        ws[b] = wt.data_ptr()
+        if isinstance(y, Partials):
+            _need(y.t, torch.float32, "partials", contiguous=False)
+            if tuple(y.t.shape[1:]) != (n, w) or y.t.stride(1) != w or y.t.stride(2) != 1:
+                raise ValueError("branch_norm_mean: partials must be [S, N, W] with dense rows")
+            ys[b], ps[b], ns[b], ss[b] = None, y.t.data_ptr(), y.nsplit, y.split_stride
+        else:
+            _need(y, out.dtype, "branch result")
+            if tuple(y.shape) != (n, w):
+                raise ValueError("branch_norm_mean: result shape")
+            ys[b], ps[b], ns[b], ss[b] = y.data_ptr(), None, 0, 0
+    name = f"kvf_branch_norm_mean_{s}"
+    _check(_fn(name, MIXERS_LIB)(ys, ps, ns, ss, ws, nb, n, w, float(eps), _ptr(out), _stream()), name)
+
+
+def softcap(logits: torch.Tensor, cap: float) -> None:
+    """``logits <- cap * tanh(logits / cap)`` in place (float)."""
+    _need(logits, torch.float32, "logits")
+    name = "kvf_softcap_f32"
+    _check(_fn(name, MIXERS_LIB)(_ptr(logits), logits.numel(), float(cap), _stream()), name)
+
+
+def rope_cache_general(
+    qkv: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor, interleaved: bool, slots: torch.Tensor | None,
+    kcache: torch.Tensor | None, vcache: torch.Tensor | None, nh: int, nkv: int, dk: int, dv: int, block_size: int,
+    err: torch.Tensor | None = None,
+) -> None:  # fmt: skip
+    """Rotary encoding and cache write in the general form: rows of ``qkv`` hold ``nh`` query heads
+    and ``nkv`` key heads of ``dk`` and ``nkv`` value heads of ``dv``; the first ``2*len(inv_freq)``
+    dims of q and k turn, pairs ``(2i, 2i+1)`` when ``interleaved`` else ``(i, i + rot/2)``; q in
+    place, k and v to ``slots`` of ``kcache [blocks, nkv, block_size, dk]`` / ``vcache [..., dv]``."""
+    s = _suffix(qkv.dtype)
+    _rows2d(qkv, None, "qkv")
+    n = qkv.shape[0]
+    if qkv.shape[1] != (nh + nkv) * dk + nkv * dv:
+        raise ValueError("rope_cache_general: qkv width")
+    _need(positions, torch.int32, "positions")
+    _need(inv_freq, torch.float32, "inv_freq")
+    rot = 2 * inv_freq.numel()
+    if rot > dk:
+        raise ValueError("rope_cache_general: more frequencies than dk/2")
+    num_slots = 0
+    if slots is not None:
+        _need(slots, torch.int32, "slots")
+        _need(kcache, qkv.dtype, "kcache")
+        _need(vcache, qkv.dtype, "vcache")
+        if tuple(kcache.shape[1:]) != (nkv, block_size, dk) or tuple(vcache.shape) != (*kcache.shape[:3], dv):
+            raise ValueError("rope_cache_general: cache shapes must be [num_blocks, nkv, block_size, dk] and [..., dv]")
+        num_slots = kcache.shape[0] * block_size
+    name = f"kvf_rope_cache_general_{s}"
+    _check(
+        _fn(name, MIXERS_LIB)(
+            _ptr(qkv), qkv.stride(0), _ptr(positions), _ptr(inv_freq), _ptr(slots), _ptr(kcache), _ptr(vcache), n, nh, nkv,
+            dk, dv, rot, 1 if interleaved else 0, block_size, num_slots, _ptr(err), _stream(),
+        ),
+        name,
+    )  # fmt: skip

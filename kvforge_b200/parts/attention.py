@@ -28,7 +28,15 @@ CLUSTER_MERGE_MAX_PAIRS = 16
 class PagedAttention(Mixer):
     """params: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``; optional
     ``position`` (a position-encoding ``PartSpec`` or ``None``), ``window`` (keys a query
-    sees, itself included; ``None`` = all) and ``scale`` (default ``1/sqrt(head_dim)``)."""
+    sees, itself included; ``None`` = all), ``scale`` (default ``1/sqrt(head_dim)``),
+    ``v_head_dim`` (size of a value head, default ``head_dim``) and ``conv`` (taps of a short causal
+    convolution over time on every channel of q, k and v, between the projection and the rotation;
+    its last ``conv - 1`` inputs are the mixer's state per request; tensors ``q_proj.conv`` ...).
+
+    Rotation of split pairs with equal key and value sizes and no convolution takes the kernels
+    of the Llama decoder; anything else (interleaved pairs, a value size of its own, a convolution)
+    goes through ``forward_general``: one product, the convolution, the general rotary kernel, and
+    the attention kernel that takes the shape."""
 
     def __init__(self, params, prefix=""):
         super().__init__(params, prefix)
@@ -48,23 +56,40 @@ class PagedAttention(Mixer):
             pos = PartSpec(pos["kind"], pos.get("params", {}))
         self.position_spec: PartSpec | None = pos
         self.position = None  # shared instance, set by the model before bind
+        self.dv = int(params.get("v_head_dim") or self.d)
+        ops.check_head_dim(self.dv)
+        self.taps = int(params.get("conv") or 0)
+        if self.taps < 0:
+            raise ValueError("conv must be a number of taps")
         self.q_dim = self.nh * self.d
-        self.qkv_dim = (self.nh + 2 * self.nkv) * self.d
+        self.o_dim = self.nh * self.dv
+        self.qkv_dim = (self.nh + self.nkv) * self.d + self.nkv * self.dv
 
     @classmethod
     def weight_decls(cls, params):
         h, nh, nkv, d = (int(params[k]) for k in ("hidden_size", "num_heads", "num_kv_heads", "head_dim"))
-        return {
+        dv = int(params.get("v_head_dim") or d)
+        taps = int(params.get("conv") or 0)
+        out = {
             "q_proj.weight": WeightDecl((nh * d, h)),
             "k_proj.weight": WeightDecl((nkv * d, h)),
-            "v_proj.weight": WeightDecl((nkv * d, h)),
-            "o_proj.weight": WeightDecl((h, nh * d)),
+            "v_proj.weight": WeightDecl((nkv * dv, h)),
+            "o_proj.weight": WeightDecl((h, nh * dv)),
         }
+        if taps:
+            out["q_proj.conv"] = WeightDecl((nh * d, taps), kind="vector", init="conv")
+            out["k_proj.conv"] = WeightDecl((nkv * d, taps), kind="vector", init="conv")
+            out["v_proj.conv"] = WeightDecl((nkv * dv, taps), kind="vector", init="conv")
+        return out
 
     def cache_need(self) -> CacheNeed:
+        v = None if self.dv == self.d else self.dv
         if self.window is None:
-            return CacheNeed("full", self.nkv, self.d, None)
-        return CacheNeed("window", self.nkv, self.d, int(self.window))
+            return CacheNeed("full", self.nkv, self.d, None, v)
+        return CacheNeed("window", self.nkv, self.d, int(self.window), v)
+
+    def state_shape(self):
+        return ((self.taps - 1) * self.qkv_dim,) if self.taps > 1 else None
 
     def bind(self, weights, rt):
         super().bind(weights, rt)
@@ -74,7 +99,10 @@ class PagedAttention(Mixer):
         self._tickets = torch.zeros(max(1, rt.max_seqs) * self.nkv, dtype=torch.int32, device=rt.device)
         # the kernel of prompts and mixed batches takes its tiles of queries from a list made with the step
         self._query_tile = None
-        if ops.tcgen05_attention_supported(rt.dtype, self.nh, self.nkv, self.d, False):
+        self.w_conv = None
+        if self.taps:
+            self.w_conv = torch.cat([weights["q_proj.conv"], weights["k_proj.conv"], weights["v_proj.conv"]], dim=0).contiguous()
+        if self.dv == self.d and ops.tcgen05_attention_supported(rt.dtype, self.nh, self.nkv, self.d, False):
             self._query_tile = ops.tcgen05_query_tile(self.nh, self.nkv)
             rt.query_tile_sizes.add(self._query_tile)
         if self.position_spec is not None and self.position is None:
@@ -83,6 +111,8 @@ class PagedAttention(Mixer):
         table = self.position.table() if self.position is not None else None
         # no table: q and k are stored and used as the projections leave them
         self.inv_freq = table if table is not None else torch.empty(0, dtype=torch.float32, device=rt.device)
+        self.interleaved = bool(getattr(self.position, "pairs_interleaved", False))
+        self.general = bool(self.taps) or self.dv != self.d or self.interleaved
 
     def _scratch(self, ctx):
         rt = self.rt
@@ -95,7 +125,7 @@ class PagedAttention(Mixer):
         split = ops.attention_split_size(ctx.num_seqs if rt.dtype == torch.bfloat16 else 1, self.nkv, bound, reach, self.d)
         # made for the smallest range size, so that one buffer serves every batch size
         smallest = min(ops.attention_split_size(1, 1, bound), ops.attention_split_size(ops.ATTN_SHORT_RANGE_PAIRS[0], 1, bound))
-        sa, sm = ops.attention_scratch_shapes(max(rt.max_seqs, ctx.num_seqs), self.nh, self.d, bound, smallest)
+        sa, sm = ops.attention_scratch_shapes(max(rt.max_seqs, ctx.num_seqs), self.nh, self.dv, bound, smallest)
         acc = rt.buf("attn.part_acc", sa[0] * sa[1] * sa[2], sa[3], torch.float32, cap=0).view(sa)
         ml = rt.buf("attn.part_ml", sm[0] * sm[1] * sm[2], sm[3], torch.float32, cap=0).view(sm)
         if self._tickets.numel() < sa[0] * self.nkv:
@@ -109,6 +139,8 @@ class PagedAttention(Mixer):
         n = x.shape[0]
         if cache is None:
             raise RuntimeError("paged_attention needs a cache")
+        if self.general:
+            return self.forward_general(ctx, x, cache)
         skinny = ops.skinny_ok(x, self.w_qkv)
         if cache.writable:
             slots = ctx.slot_mappings[cache.group]
@@ -138,9 +170,31 @@ class PagedAttention(Mixer):
         self.attend(ctx, q, q_stride, out, cache)
         return project(rt, "attn.proj", out, self.w_o, ctx)
 
+    def forward_general(self, ctx, x: torch.Tensor, cache):
+        rt = self.rt
+        n = x.shape[0]
+        if not cache.writable:
+            raise RuntimeError("a mixer in the general form keeps its own keys and values")
+        qkv = rt.buf("attn.qkv", n, self.qkv_dim)
+        if ops.skinny_ok(x, self.w_qkv):
+            ops.gemm_skinny(x, self.w_qkv, qkv)
+        else:
+            ops.linear(x, self.w_qkv, qkv)
+        if self.taps:
+            mixed = rt.buf("attn.qkv_conv", n, self.qkv_dim)
+            ops.causal_conv(qkv, self.w_conv, cache.state, ctx.query_start_loc, ctx.state_slots, ctx.num_seqs, mixed)
+            qkv = mixed
+        ops.rope_cache_general(
+            qkv, ctx.positions, self.inv_freq, self.interleaved, ctx.slot_mappings[cache.group], cache.k, cache.v,
+            self.nh, self.nkv, self.d, self.dv, ctx.block_size, rt.err,
+        )  # fmt: skip
+        out = rt.buf("attn.out", n, self.o_dim)
+        self.attend(ctx, qkv, self.qkv_dim, out, cache)
+        return project(rt, "attn.proj", out, self.w_o, ctx)
+
     def attend(self, ctx, q, q_stride, out, cache) -> None:
         scratch, bound, split = None, None, 256
-        common = dict(window=int(self.window or 0), q_stride=q_stride, err=self.rt.err)
+        common = dict(window=int(self.window or 0), q_stride=q_stride, err=self.rt.err, dv=self.dv)
         args = (q, out, cache.k, cache.v, ctx.block_tables[cache.group], ctx.query_start_loc, ctx.context_lens, ctx.num_seqs)
         shape = (self.nh, self.nkv, self.d, self.scale)
         # bfloat16: the decode kernel may lengthen its key ranges from the step's longest context (the merge
@@ -149,7 +203,7 @@ class PagedAttention(Mixer):
         if ctx.all_single_query:
             scratch, bound, split = self._scratch(ctx)
         tiles = ctx.query_tiles.get(self._query_tile)
-        if tiles is not None and tiles.num_single > 0 and ops.tma_decode_supported(q.dtype, self.nh, self.nkv, self.d, ctx.block_size, cache.k.shape[0]):
+        if tiles is not None and tiles.num_single > 0 and self.dv == self.d and ops.tma_decode_supported(q.dtype, self.nh, self.nkv, self.d, ctx.block_size, cache.k.shape[0]):
             # a mixed batch: the sequences that bring one token go to the decode kernel (key ranges in
             # parallel), the portions of prompts to the kernel of prompts; each leaves the other's rows alone
             scratch, bound, split = self._scratch(ctx)

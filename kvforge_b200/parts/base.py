@@ -69,10 +69,15 @@ class CacheNeed:
     kv_heads: int = 0
     head_dim: int = 0
     window: int | None = None
+    v_head_dim: int | None = None  # size of a value head when it differs from a key head's
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
 
     @property
     def group_key(self) -> tuple:
-        return (self.kind, self.kv_heads, self.head_dim, self.window)
+        return (self.kind, self.kv_heads, self.head_dim, self.window, self.value_dim)
 
 
 @dataclass
@@ -89,10 +94,15 @@ class LayerCache:
     """The pages one mixer call reads and, if ``writable``, writes."""
 
     k: torch.Tensor  # [num_blocks, kv_heads, block_size, head_dim]
-    v: torch.Tensor
+    v: torch.Tensor  # [num_blocks, kv_heads, block_size, value head_dim]
     group: int  # index of the cache group: selects the block table and slots in the context
     writable: bool = True
     state: torch.Tensor | None = None  # [num_slots, *state_shape] if the mixer has state
+
+    def with_state(self, lo: int, hi: int) -> "LayerCache":
+        """The same pages with columns ``lo:hi`` of a flat state ``[num_slots, width]``: what a mixer
+        made of several parts hands each of them."""
+        return LayerCache(self.k, self.v, self.group, self.writable, None if self.state is None else self.state[:, lo:hi])
 
 
 class Part:
@@ -104,8 +114,17 @@ class Part:
 
     @classmethod
     def weight_decls(cls, params: dict[str, Any]) -> dict[str, WeightDecl]:
-        """Local tensor name -> declaration.  The checkpoint name is ``prefix + local``."""
+        """Local tensor name -> declaration.  The checkpoint name is ``prefix + local``, or
+        ``prefix + params["names"][local]`` where the model's checkpoints call the tensor otherwise."""
         return {}
+
+    def tensor_name(self, local: str) -> str:
+        """Checkpoint name of the tensor this part calls ``local``."""
+        return self.prefix + (self.params.get("names") or {}).get(local, local)
+
+    def sub_parts(self) -> list["Part"]:
+        """Parts this part is made of (their tensors are loaded and bound with it)."""
+        return []
 
     def bind(self, weights: dict[str, torch.Tensor], rt: Any) -> None:
         """Take the device tensors (keyed by local name) and whatever else the run needs."""

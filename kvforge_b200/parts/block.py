@@ -8,13 +8,20 @@ hands back its own.
 
 from __future__ import annotations
 
-from .base import Block, PartSpec, build_part, register_block
+from .. import ops
+from .base import Block, PartSpec, WeightDecl, build_part, register_block
 
 
 def _spec(v) -> PartSpec:
     if isinstance(v, PartSpec):
         return v
     return PartSpec(v["kind"], v.get("params", {}))
+
+
+def _stem(prefix: str, name: str) -> str:
+    """Prefix of a sub-part's tensors: ``<layer prefix><name>.``, or the layer's own prefix for an
+    empty name (the part's ``names`` then give its tensors' whole names under the layer)."""
+    return f"{prefix}{name}." if name else prefix
 
 
 @register_block("prenorm")
@@ -30,10 +37,10 @@ class PreNormBlock(Block):
             "norm2": params.get("norm2_name", "post_attention_layernorm"),
             "ffn": params.get("ffn_name", "mlp"),
         }
-        self.norm1 = build_part("norm", _spec(params["norm1"]), f"{prefix}{names['norm1']}.")
-        self.mixer = build_part("mixer", _spec(params["mixer"]), f"{prefix}{names['mixer']}.")
-        self.norm2 = build_part("norm", _spec(params["norm2"]), f"{prefix}{names['norm2']}.")
-        self.ffn = build_part("ffn", _spec(params["ffn"]), f"{prefix}{names['ffn']}.")
+        self.norm1 = build_part("norm", _spec(params["norm1"]), _stem(prefix, names["norm1"]))
+        self.mixer = build_part("mixer", _spec(params["mixer"]), _stem(prefix, names["mixer"]))
+        self.norm2 = build_part("norm", _spec(params["norm2"]), _stem(prefix, names["norm2"]))
+        self.ffn = build_part("ffn", _spec(params["ffn"]), _stem(prefix, names["ffn"]))
 
     def sub_parts(self):
         return [self.norm1, self.mixer, self.norm2, self.ffn]
@@ -46,3 +53,72 @@ class PreNormBlock(Block):
         a = self.mixer.forward(ctx, x, cache)
         x = self.norm2.forward(ctx, resid, a)
         return self.ffn.forward(ctx, x)
+
+
+@register_block("stream_prenorm")
+class StreamPreNormBlock(Block):
+    """The pre-norm arrangement over several residual streams (hyper-connections).  A token has
+    ``S`` streams ``x_1 .. x_S``; sublayer ``q`` (1: the mixer, 2: the feed-forward) reads
+    ``u = sum_s in_q[s] x_s``, computes ``y = f(norm_q(u))`` and writes, for all ``t`` from the old
+    streams, ``x_t <- sum_s mix_q[s, t] x_s + out_q[t] y``.  A write is folded into the read that
+    follows it (one kernel), so the block takes the write still pending from the block before and
+    hands back its own.
+
+    params: ``streams``, ``norm1``, ``mixer``, ``norm2``, ``ffn`` (``PartSpec`` each; ``ffn`` and
+    ``norm2`` may be ``None``: a layer without a feed-forward), the stems ``norm1_name``,
+    ``mixer_name``, ``norm2_name``, ``ffn_name``, and ``hc1_name`` / ``hc2_name`` under which the
+    float tensors ``in [S]``, ``out [S]`` and ``mix [S, S]`` (from, to) of each sublayer lie."""
+
+    def __init__(self, params, prefix=""):
+        super().__init__(params, prefix)
+        self.streams = int(params["streams"])
+        if not 0 < self.streams <= ops.MAX_STREAMS:
+            raise ValueError(f"between 1 and {ops.MAX_STREAMS} residual streams")
+        self.norm1 = build_part("norm", _spec(params["norm1"]), _stem(prefix, params.get("norm1_name", "norm1")))
+        self.mixer = build_part("mixer", _spec(params["mixer"]), _stem(prefix, params.get("mixer_name", "mix")))
+        self.ffn = self.norm2 = None
+        if params.get("ffn") is not None:
+            self.norm2 = build_part("norm", _spec(params["norm2"]), _stem(prefix, params.get("norm2_name", "norm2")))
+            self.ffn = build_part("ffn", _spec(params["ffn"]), _stem(prefix, params.get("ffn_name", "mlp")))
+
+    @classmethod
+    def weight_decls(cls, params):
+        s = int(params["streams"])
+        out = {}
+        for key, default in (("hc1_name", "hc1"), ("hc2_name", "hc2")):
+            if default == "hc2" and params.get("ffn") is None:
+                continue
+            stem = params.get(key, default)
+            out[f"{stem}.in"] = WeightDecl((s,), kind="vector", init="ones")
+            out[f"{stem}.out"] = WeightDecl((s,), kind="vector", init="ones")
+            out[f"{stem}.mix"] = WeightDecl((s, s), kind="vector", init="eye")
+        return out
+
+    def bind(self, weights, rt):
+        super().bind(weights, rt)
+        p = self.params
+        self.hc = []
+        for key, default in (("hc1_name", "hc1"), ("hc2_name", "hc2")):
+            stem = p.get(key, default)
+            if f"{stem}.in" in weights:
+                self.hc.append(tuple(weights[f"{stem}.{k}"].contiguous() for k in ("in", "mix", "out")))
+
+    def sub_parts(self):
+        return [p for p in (self.norm1, self.mixer, self.norm2, self.ffn) if p is not None]
+
+    def mixer_part(self):
+        return self.mixer
+
+    def forward(self, ctx, resid, delta, cache):
+        keep, ctx.residual = ctx.residual, None  # no part may add into one of several streams by itself
+        try:
+            read, mix, out = self.hc[0]
+            x = self.norm1.forward(ctx, resid, delta, read=read)
+            pending = ops.StreamWrite(self.mixer.forward(ctx, x, cache), mix, out)
+            if self.ffn is not None:
+                read, mix, out = self.hc[1]
+                x = self.norm2.forward(ctx, resid, pending, read=read)
+                pending = ops.StreamWrite(self.ffn.forward(ctx, x), mix, out)
+        finally:
+            ctx.residual = keep
+        return pending

@@ -12,13 +12,17 @@ from .base import Head, WeightDecl, register_head
 
 @register_head("linear_head")
 class LinearHead(Head):
-    """params: ``vocab_size``, ``hidden_size``.  Its tensor is optional in a checkpoint."""
+    """params: ``vocab_size``, ``hidden_size``; optional ``softcap`` (``c``: the logits become
+    ``c * tanh(logits / c)``).  Its tensor is optional in a checkpoint."""
 
     def __init__(self, params, prefix=""):
         super().__init__(params, prefix)
         self.vocab = int(params["vocab_size"])
         self.hidden = int(params["hidden_size"])
         self.weight = None
+        self.softcap = float(params.get("softcap") or 0.0)
+        if self.softcap < 0:
+            raise ValueError("softcap must be positive")
 
     @classmethod
     def weight_decls(cls, params):
@@ -39,4 +43,6 @@ class LinearHead(Head):
             ops.gemm_skinny(x, self.weight, logits)
         else:
             ops.linear(x, self.weight, logits)
+        if self.softcap:
+            ops.softcap(logits, self.softcap)
         return logits

@@ -15,6 +15,7 @@ from dataclasses import dataclass, field
 
 import torch
 
+from .. import ops
 from . import embedding as _embedding, head as _head  # noqa: F401  (register the default parts)
 from .base import Block, CacheNeed, LayerCache, PartSpec, WeightDecl, build_part
 
@@ -57,6 +58,9 @@ class ModelSpec:
     input_position_prefix: str = "model.embed_positions."
     eos_token_id: int | None = None
     bos_token_id: int | None = None
+    # how many residual streams a token has (hyper-connections); the blocks' arrangement reads and writes
+    # them, all start as the embedding's output, and the final norm reads their sum
+    residual_streams: int = 1
 
     def __post_init__(self) -> None:
         if not self.execution:
@@ -88,11 +92,17 @@ class DecoderModel:
         self.blocks: list[Block] = [build_part("block", ls.block, ls.prefix) for ls in spec.layers]
         self.final_norm = build_part("norm", spec.final_norm, spec.final_norm_prefix)
         sizes = {"vocab_size": spec.vocab_size, "hidden_size": spec.hidden_size}
-        for name in (spec.embedding_name, spec.lm_head_name):
-            if not name.endswith("weight"):
-                raise ValueError(f"tensor name {name!r} must end in 'weight'")
-        self.embedding = build_part("embedding", spec.embedding or PartSpec("token_embedding", sizes), spec.embedding_name[: -len("weight")])
-        self.head = build_part("head", spec.head or PartSpec("linear_head", sizes), spec.lm_head_name[: -len("weight")])
+
+        def named(part_spec: PartSpec, tensor: str) -> tuple[PartSpec, str]:
+            # the part calls its tensor "weight"; a checkpoint name that does not end so is given whole
+            if tensor.endswith("weight"):
+                return part_spec, tensor[: -len("weight")]
+            return PartSpec(part_spec.kind, {**part_spec.params, "names": {"weight": tensor}}), ""
+
+        self.embedding = build_part("embedding", *named(spec.embedding or PartSpec("token_embedding", sizes), spec.embedding_name))
+        self.head = build_part("head", *named(spec.head or PartSpec("linear_head", sizes), spec.lm_head_name))
+        if spec.residual_streams < 1:
+            raise ValueError("residual_streams must be at least 1")
         self.input_position = build_part("position", spec.input_position, spec.input_position_prefix) if spec.input_position else None
         # cache groups from what the mixers declare
         self.groups: list[CacheGroup] = []
@@ -130,14 +140,22 @@ class DecoderModel:
         out: dict[str, WeightDecl] = {}
         for part in self._all_parts():
             for local, decl in type(part).weight_decls(part.params).items():
-                out[part.prefix + local] = decl
+                out[part.tensor_name(local)] = decl
         return out
 
     def _all_parts(self):
+        def walk(part):
+            yield part
+            for sub in part.sub_parts():
+                yield from walk(sub)
+
         yield self.embedding
         yield self.head
         for block in self.blocks:
-            yield from block.sub_parts()
+            for part in block.sub_parts():
+                yield from walk(part)
+            if type(block).weight_decls(block.params):
+                yield block  # an arrangement with tensors of its own
         yield self.final_norm
         if self.input_position is not None:
             yield self.input_position
@@ -155,11 +173,11 @@ class DecoderModel:
                     inst.bind({}, rt)
                     shared_positions[key] = inst
                 part.position = shared_positions[key]
-            local = {name: weights[part.prefix + name] for name in type(part).weight_decls(part.params) if part.prefix + name in weights}
+            local = {name: weights[part.tensor_name(name)] for name in type(part).weight_decls(part.params) if part.tensor_name(name) in weights}
             part.bind(local, rt)
         # kvforge: one tensor when tied, and the embedding stands in when the head is absent
         # (src/tokenvault/model.py:157-158, src/tokenvault/model_loader.py:105-106)
-        if s.tie_word_embeddings or s.lm_head_name not in weights:
+        if s.tie_word_embeddings or self.head.tensor_name("weight") not in weights:
             self.head.tie(self.embedding.table())
 
     def attach_cache(self, caches: list[LayerCache | None]) -> None:
@@ -177,6 +195,11 @@ class DecoderModel:
         ctx.residual = resid
         if self.input_position is not None:
             self.input_position.embed(ctx, resid)
+        if self.spec.residual_streams > 1:
+            # every stream starts as the embedding's output; no part may add into a single stream
+            streams = rt.buf("model.streams", ctx.num_tokens, self.spec.residual_streams * self.spec.hidden_size, torch.float32)
+            ops.replicate_streams(resid, streams, self.spec.residual_streams)
+            resid, ctx.residual = streams, None
         delta = None
         for idx, call in enumerate(self.spec.execution):
             delta = self.blocks[call.layer].forward(ctx, resid, delta, self.caches[idx])

@@ -36,3 +36,33 @@ class RMSNorm(Norm):
         out = self.rt.buf("norm.out" if rows is None else "norm.rows", n, self.dim)
         ops.add_rmsnorm(resid, delta, self.weight, out, self.eps, rows)
         return out
+
+
+@register_norm("stream_rmsnorm")
+class StreamRMSNorm(Norm):
+    """RMSNorm of a read-out of several residual streams ``[N, S*dim]``.  params: ``dim``, ``eps``,
+    ``streams``.  ``forward`` takes the write that the sublayer before left pending (an
+    ``ops.StreamWrite`` or ``None``), moves the streams on, and norms ``sum_t read[t] x_t``
+    (``read=None``: the plain sum, what a model's final norm reads)."""
+
+    def __init__(self, params, prefix=""):
+        super().__init__(params, prefix)
+        self.dim = int(params["dim"])
+        self.eps = float(params["eps"])
+        self.streams = int(params["streams"])
+
+    @classmethod
+    def weight_decls(cls, params):
+        return {"weight": WeightDecl((int(params["dim"]),), kind="vector", init="ones")}
+
+    def bind(self, weights, rt):
+        super().bind(weights, rt)
+        self.weight = weights["weight"]
+
+    def forward(self, ctx, resid: torch.Tensor, delta, rows: torch.Tensor | None = None, num_rows: int | None = None, read: torch.Tensor | None = None):
+        if delta is ops.ADDED:
+            raise RuntimeError("a part added into the residual stream of a model that has several")
+        n = num_rows if rows is not None else resid.shape[0]
+        out = self.rt.buf("norm.out" if rows is None else "norm.rows", n, self.dim)
+        ops.stream_step(resid, delta, read, self.weight, out, self.eps, self.streams, rows)
+        return out

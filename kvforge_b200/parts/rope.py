@@ -36,8 +36,10 @@ def llama3_scale(inv_freq: torch.Tensor, factor: float, low_freq_factor: float, 
 @register_position_encoding("rotary")
 class RotaryEmbedding(PositionEncoding):
     """params: ``head_dim``, ``theta``, optional ``rotary_dim`` (leading dims that turn;
-    default all) and ``scaling`` (``None`` or the llama3 dict: ``factor``,
-    ``low_freq_factor``, ``high_freq_factor``, ``original_max_position_embeddings``)."""
+    default all), ``scaling`` (``None`` or the llama3 dict: ``factor``,
+    ``low_freq_factor``, ``high_freq_factor``, ``original_max_position_embeddings``) and
+    ``interleaved`` (the pairs that turn are dims ``(2i, 2i+1)`` instead of ``(i, i + rot/2)``; a
+    mixer asks ``pairs_interleaved`` and tells its kernel)."""
 
     def __init__(self, params, prefix=""):
         super().__init__(params, prefix)
@@ -47,6 +49,7 @@ class RotaryEmbedding(PositionEncoding):
             raise ValueError(f"rotary_dim {self.rotary_dim} must be even and at most head_dim {self.head_dim}")
         self.theta = float(params["theta"])
         self.scaling = params.get("scaling")
+        self.pairs_interleaved = bool(params.get("interleaved", False))
 
     def inv_freq_host(self) -> torch.Tensor:
         inv = rotary_inv_freq(self.rotary_dim, self.theta)

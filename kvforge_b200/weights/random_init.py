@@ -41,6 +41,15 @@ def draw(name: str, decl: WeightDecl, seed: int, device: torch.device | str = "c
         if norm_std:
             t += norm_std * torch.randn(decl.shape, generator=g, dtype=torch.float32, device=device)
         return t
+    if decl.init == "eye":  # a mixing matrix near the identity
+        t = torch.eye(decl.shape[0], decl.shape[1], dtype=torch.float32, device=device)
+        return t + (norm_std or 0.1) * torch.randn(decl.shape, generator=g, dtype=torch.float32, device=device)
+    if decl.init == "conv":  # taps of a short convolution: of order one, so that the signal passes
+        return 0.5 * torch.randn(decl.shape, generator=g, dtype=torch.float32, device=device)
+    if decl.init == "small":  # logarithms of rates and biases of step sizes: of order one
+        return 0.5 * torch.randn(decl.shape, generator=g, dtype=torch.float32, device=device)
+    if decl.init == "wide":  # the second matrix of a low-rank pair: its input is small already
+        return (decl.shape[-1] ** -0.5) * torch.randn(decl.shape, generator=g, dtype=torch.float32, device=device)
     return init_std * torch.randn(decl.shape, generator=g, dtype=torch.float32, device=device)
 
 
