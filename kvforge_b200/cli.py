@@ -55,9 +55,9 @@ def main() -> int:
     tokenizer = None
     if args.prompt:  # text goes in as bytes, fitted to the vocabulary of the model that will run
         if args.hf_model:
-            from .config.model_config import read_config_json
+            from .engine.core import spec_from_model_dir
 
-            vocab = int(read_config_json(args.hf_model)["vocab_size"])
+            vocab = spec_from_model_dir(args.hf_model)[1].vocab_size
         else:
             vocab = PRESETS[args.preset].vocab_size
         tokenizer = ByteTokenizer(vocab)

@@ -197,3 +197,35 @@ class MopilornConfig:
         if self.logit_softcap:
             out["logit_softcap"] = self.logit_softcap
         return out
+
+
+def alternating(
+    *, vocab: int, width: int, num_layers: int, ff: int, streams: int | None, attn_heads: int, attn_kv_heads: int, dim: int, vdim: int,
+    window: int | None, delta_heads: int, channel_heads: int, rank: int, conv: int = 4, rot_dims: int | None = None, base: float = 10000.0,
+    eps: float = 1e-6, logit_softcap: float | None = 30.0,
+) -> MopilornConfig:  # fmt: skip
+    """A configuration whose layers alternate between the two mixers (the first is ``parallel``), with
+    the same sizes in every layer of a kind: what the named shapes below are made with."""
+    left = AttentionConfig(attn_heads, attn_kv_heads, dim, vdim, conv, dim**-0.5, window, RotaryConfig(rot_dims or dim, base, None))
+    right = DeltaConfig(delta_heads, delta_heads, dim, vdim, conv)
+    channel = DeltaConfig(channel_heads, channel_heads, dim, vdim, conv, rank, rank)
+    layers = [LayerConfig("parallel", left, right, ff) if i % 2 == 0 else LayerConfig("channel_delta", None, channel, ff) for i in range(num_layers)]
+    return MopilornConfig(vocab, width, streams, eps, logit_softcap, layers)
+
+
+# Named shapes with random weights: a small one for demonstrations, and two with the widths of the Llama
+# shapes this engine is measured on (equal width, layers, feed-forward and vocabulary).
+MOPILORN_PRESETS: dict[str, MopilornConfig] = {
+    "mopilorn-tiny": alternating(
+        vocab=256, width=96, num_layers=3, ff=160, streams=2, attn_heads=4, attn_kv_heads=2, dim=32, vdim=48, window=24,
+        delta_heads=2, channel_heads=3, rank=8, conv=3, rot_dims=16,
+    ),
+    "mopilorn-1b": alternating(
+        vocab=128256, width=2048, num_layers=16, ff=8192, streams=4, attn_heads=16, attn_kv_heads=4, dim=128, vdim=128, window=1024,
+        delta_heads=8, channel_heads=16, rank=64, rot_dims=64, base=500000.0,
+    ),
+    "mopilorn-3b": alternating(
+        vocab=128256, width=3072, num_layers=28, ff=8192, streams=4, attn_heads=24, attn_kv_heads=8, dim=128, vdim=128, window=2048,
+        delta_heads=8, channel_heads=24, rank=96, rot_dims=64, base=500000.0,
+    ),
+}  # fmt: skip

@@ -73,7 +73,7 @@ def _ensure_builtin() -> None:
 _LLAMA3_32 = RopeScaling(factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0, original_max_position_embeddings=8192)
 _LLAMA3_8 = RopeScaling(factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0, original_max_position_embeddings=8192)
 
-PRESETS: dict[str, ModelConfig] = {
+PRESETS: dict[str, Any] = {
     "tiny-a": ModelConfig(
         vocab_size=256, hidden_size=64, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=16,
         intermediate_size=192, rms_norm_eps=1e-5, rope_theta=10000.0, tie_word_embeddings=True,
@@ -104,3 +104,7 @@ PRESETS: dict[str, ModelConfig] = {
 # kvforge's own preset name for the 1B shape (src/tokenvault/model_loader.py:28-33)
 PRESETS["llama-1b"] = PRESETS["llama-3.2-1b"]
 PRESETS["llama-8b"] = PRESETS["llama-3.1-8b"]
+
+from .mopilorn_config import MOPILORN_PRESETS  # noqa: E402
+
+PRESETS.update(MOPILORN_PRESETS)

@@ -419,8 +419,8 @@ def attention_scratch_shapes(max_seqs: int, nh: int, d: int, max_context: int, s
 
 
 def check_head_dim(d: int) -> None:
-    if d <= 0 or d % 16 != 0 or d > 256:
-        raise ValueError(f"head_dim {d} is not supported: it must be a multiple of 16, at most 256")
+    if d <= 0 or d % 8 != 0 or d > 256:
+        raise ValueError(f"head_dim {d} is not supported: it must be a multiple of 8, at most 256")
 
 
 def mma_attention_supported(dtype: torch.dtype, nh: int, nkv: int, d: int, decode_form: bool) -> bool:

@@ -122,14 +122,12 @@ class GatedDeltaRule(Mixer):
             return torch.cat(rows, dim=0).contiguous(), offs
 
         # one product in the storage type: q, k, v, then what feeds the gate and a low-rank decay
-        main = [W["q"], W["k"], W["v"], W["g1"] if self.gate_rank else W["g"]]
+        main = [torch.cat([W["q"], W["k"], W["v"]], dim=0), W["g1"] if self.gate_rank else W["g"]]
         if self.decay_rank:
             main.append(W["a1"])
         self.w_main, offs = stack(main)
-        if self.c_qkv % 8 or offs[2] != 2 * self.c_q:
-            raise ValueError("gated_delta_rule: kv_heads * head_dim must be a multiple of 8")
-        self.off_gate = offs[3]
-        self.off_a1 = offs[4] if self.decay_rank else None
+        self.off_gate = offs[1]
+        self.off_a1 = offs[2] if self.decay_rank else None
         # one product with a float result: the logits of beta, and of the step size when they come straight from h
         small = [W["b"]] if self.decay_rank else [W["b"], W["a"]]
         self.w_small, soffs = stack(small)

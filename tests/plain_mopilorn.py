@@ -208,12 +208,35 @@ def hyper_sublayer(streams: torch.Tensor, fn, norm_w, eps: float, w_in, w_mix, w
     return torch.einsum("sr,stw->rtw", w_mix, streams) + w_out[:, None, None] * y[None]
 
 
+def output(cfg: dict, w: dict, x: torch.Tensor, eps: float) -> torch.Tensor:
+    logits = rms_norm(x, w["final.norm"], eps) @ w["head"].T
+    cap = cfg.get("logit_softcap")
+    if cap:
+        logits = float(cap) * torch.tanh(logits / float(cap))
+    return logits
+
+
+def _forward_single_stream(cfg, w, x, eps, return_layers):
+    """Without streams: x <- x + mixer(norm1(x)); x <- x + ff(norm2(x))."""
+    per_layer = []
+    for i, layer in enumerate(cfg["layers"]):
+        p = f"l{i}."
+        x = x + mixer(layer["type"], rms_norm(x, w[p + "norm1"], eps), w, p + "mix.", layer["mixer"], eps)
+        if layer.get("mlp"):
+            x = x + dense_ff(rms_norm(x, w[p + "norm2"], eps), w, p + "mlp.")
+        per_layer.append(x)
+    logits = output(cfg, w, x, eps)
+    return (logits, torch.stack(per_layer)) if return_layers else logits
+
+
 def forward(cfg: dict, w: dict, tokens, return_layers: bool = False):
     """Logits ``[T, vocab]`` of one whole sequence (and, on request, the sum of the streams
     after every layer, ``[layers, T, W]``)."""
     eps = float(cfg["norm"]["eps"])
-    n_streams = int(cfg.get("streams", 1))
     x = w["embed"][torch.as_tensor(tokens, dtype=torch.long)]
+    if cfg.get("streams") is None:
+        return _forward_single_stream(cfg, w, x, eps, return_layers)
+    n_streams = int(cfg["streams"])
     streams = x[None].repeat(n_streams, 1, 1)
     per_layer = []
     for i, layer in enumerate(cfg["layers"]):
@@ -230,11 +253,7 @@ def forward(cfg: dict, w: dict, tokens, return_layers: bool = False):
                 w[p + "norm2"], eps, w[p + "hc2.in"], w[p + "hc2.mix"], w[p + "hc2.out"],
             )  # fmt: skip
         per_layer.append(streams.sum(0))
-    x = streams.sum(0)
-    logits = rms_norm(x, w["final.norm"], eps) @ w["head"].T
-    cap = cfg.get("logit_softcap")
-    if cap:
-        logits = float(cap) * torch.tanh(logits / float(cap))
+    logits = output(cfg, w, streams.sum(0), eps)
     if return_layers:
         return logits, torch.stack(per_layer)
     return logits
