@@ -37,31 +37,104 @@ __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log
 // y[n, c] = act( sum_j w[c, j] * u[t - (taps-1) + j, c] ), t the place of row n in its sequence; places
 // before this step's first row come from the state (the last taps-1 inputs of the sequence, oldest
 // first, [taps-1][C] floats), which is zero before a sequence's start.
-template <typename T>
-__global__ void __launch_bounds__(256) causal_conv_kernel(const T* __restrict__ x, int x_stride, const float* __restrict__ w,
+template <typename T, int VEC> struct VecIO;
+template <> struct VecIO<float, 4> {
+  static __device__ __forceinline__ void load(const float* p, float* f) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float* f) { *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]); }
+};
+template <> struct VecIO<bf16, 8> {
+  static __device__ __forceinline__ void load(const bf16* p, float* f) { bf16x8_to_float(*reinterpret_cast<const uint4*>(p), f); }
+  static __device__ __forceinline__ void store(bf16* p, const float* f) {
+    uint4 u;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = u;
+  }
+};
+template <typename T> struct VecIO<T, 1> {
+  static __device__ __forceinline__ void load(const T* p, float* f) { f[0] = to_float<T>(p[0]); }
+  static __device__ __forceinline__ void store(T* p, const float* f) { p[0] = from_float<T>(f[0]); }
+};
+
+// A thread owns VEC neighbouring channels (one 16-byte load) of `rows` consecutive token rows; TAPS > 0: the
+// taps are known at compile time and a thread keeps its weights in registers.  Each output is one chain of
+// fused multiply-adds over the taps, oldest first, whichever form runs.
+template <typename T, int VEC, int TAPS>
+__global__ void __launch_bounds__(128) causal_conv_kernel(const T* __restrict__ x, int x_stride, const float* __restrict__ w,
                                                           const float* __restrict__ state, long long state_stride,
                                                           const int* __restrict__ qsl, const int* __restrict__ state_slots,
-                                                          int B, int C, int taps, int act, T* __restrict__ out, int out_stride) {
-  const int n = blockIdx.x;
-  const int b = seq_of_row(qsl, B, n);
-  if (b < 0) return;
-  const int slot = state_slots[b];
-  const int first = qsl[b];
-  const int t = n - first;
-  const float* st = slot >= 0 ? state + (size_t)slot * state_stride : nullptr;
-  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
-    float acc = 0.f;
-    for (int j = 0; j < taps; ++j) {
+                                                          int N, int B, int C, int taps_rt, int act, T* __restrict__ out,
+                                                          int out_stride, int rows) {
+  const int taps = TAPS > 0 ? TAPS : taps_rt;
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * VEC;
+  if (c >= C) return;
+  float wr[VEC][TAPS > 0 ? TAPS : 1];
+  if (TAPS > 0) {
+#pragma unroll
+    for (int e = 0; e < VEC; ++e)
+#pragma unroll
+      for (int j = 0; j < TAPS; ++j) wr[e][j] = w[(size_t)(c + e) * TAPS + j];
+  }
+  for (int rr = 0; rr < rows; ++rr) {
+    const int n = blockIdx.x * rows + rr;
+    if (n >= N) return;
+    const int b = seq_of_row(qsl, B, n);
+    if (b < 0) return;  // this row and all after it belong to no sequence
+    const int slot = state_slots[b];
+    const int first = qsl[b];
+    const int t = n - first;
+    const float* st = slot >= 0 ? state + (size_t)slot * state_stride : nullptr;
+    float acc[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) acc[e] = 0.f;
+#pragma unroll
+    for (int j = 0; j < (TAPS > 0 ? TAPS : 64); ++j) {
+      if (j >= taps) break;
       const int src = t - (taps - 1) + j;
-      float u;
-      if (src >= 0) u = to_float<T>(x[(size_t)(first + src) * x_stride + c]);
-      else u = st ? st[(size_t)(taps - 1 + src) * C + c] : 0.f;
-      acc = fmaf(w[(size_t)c * taps + j], u, acc);
+      float u[VEC];
+      if (src >= 0) {
+        VecIO<T, VEC>::load(x + (size_t)(first + src) * x_stride + c, u);
+      } else {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) u[e] = st ? st[(size_t)(taps - 1 + src) * C + c + e] : 0.f;
+      }
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) acc[e] = fmaf(TAPS > 0 ? wr[e][TAPS > 0 ? j : 0] : w[(size_t)(c + e) * taps + j], u[e], acc[e]);
     }
-    if (act == 1) acc = silu_f(acc);
-    out[(size_t)n * out_stride + c] = from_float<T>(acc);
+    if (act == 1) {
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) acc[e] = silu_f(acc[e]);
+    }
+    VecIO<T, VEC>::store(out + (size_t)n * out_stride + c, acc);
   }
 }
+
+template <typename T, int VEC>
+int launch_conv(const T* x, int x_stride, const float* w, const float* state, long long state_stride, const int* qsl,
+                const int* state_slots, int N, int B, int C, int taps, int act, T* out, int out_stride, cudaStream_t st) {
+  const int rows = N >= 1024 ? 4 : 1;
+  const int per_cta = 128 * VEC;
+  dim3 grid((N + rows - 1) / rows, (C + per_cta - 1) / per_cta);
+  if (grid.y > 65535u) return (int)cudaErrorInvalidValue;
+#define KVF_CONV_CASE(TP)                                                                                             \
+  causal_conv_kernel<T, VEC, TP><<<grid, 128, 0, st>>>(x, x_stride, w, state, state_stride, qsl, state_slots, N, B, C, \
+                                                        taps, act, out, out_stride, rows)
+  if (taps == 2) KVF_CONV_CASE(2);
+  else if (taps == 3) KVF_CONV_CASE(3);
+  else if (taps == 4) KVF_CONV_CASE(4);
+  else if (taps <= 64) KVF_CONV_CASE(0);
+  else return (int)cudaErrorInvalidValue;
+#undef KVF_CONV_CASE
+  return KVF_LAUNCH_STATUS();
+}
+
+template <typename T> struct ConvVec;
+template <> struct ConvVec<float> { static constexpr int N = 4; };
+template <> struct ConvVec<bf16> { static constexpr int N = 8; };
 
 // The state after the step: the last taps-1 inputs of each sequence, old ones moved up where the
 // step brought fewer rows than that.  Entry i is read at i + q_len > i before entry i is written,
@@ -93,11 +166,17 @@ __global__ void __launch_bounds__(256) conv_state_kernel(const T* __restrict__ x
 // with k and q made unit vectors per head (x / sqrt(sum x^2 + norm_eps)), q times q_scale,
 // beta = sigmoid(b), g = exp(-exp(A_log[h]) * softplus(a + dt_bias)).
 //
-// A CTA owns a sequence, a head and a tile of columns of S; a thread owns R rows (r = i*KS + ks) of one
-// column in registers, so the KS threads of a column are neighbours in a warp and the two dot products
-// of a token are R fused multiply-adds and a shuffle tree.  Tokens come in chunks: the CTA loads and
-// prepares a chunk's k, q, v, beta and g into shared memory together, then walks the chunk without a
-// barrier.
+// The walk over a sequence's tokens is a chain: a token's update needs the state the token before
+// left.  What bounds it is the latency of one link, so a link is made short.  A CTA owns a sequence,
+// a head and a tile of columns of S; a column's rows are spread over KS neighbouring lanes, R rows
+// each, in registers.  One pass over a thread's rows applies the decay and takes both dot products
+// with the decayed state, (S^T k) and (S^T q), in split accumulators; two shuffle trees run side by
+// side; then u = beta (v - S^T k), the read-out is o = S^T q + u (k . q) (the same as reading after
+// the write, with k . q taken once per token), and the write is one fused multiply-add per row with
+// the keys still in registers.  Tokens come in chunks through two buffers of shared memory: four
+// producer warps load a chunk's k, q, v and logits with all their loads in flight at once, norm
+// them, and compute beta, g and k . q, while the consumer warps walk the chunk before.  The state
+// goes through shared memory on its way in and out, so that global memory sees whole rows of a tile.
 struct DeltaParams {
   const void* q;  // [N][G*dk] after convolution and activation
   const void* k;
@@ -118,149 +197,294 @@ struct DeltaParams {
   const int* state_slots;
   int H, G, dk, dv;
   float q_scale, norm_eps;
-  int chunk;  // tokens per chunk
+  int chunk;       // tokens per chunk (a multiple of the producer warps)
+  int buf_floats;  // floats of one chunk buffer
 };
 
-template <typename T, int R, int KS>
-__global__ void __launch_bounds__(R * KS > 512 ? 1024 : 256) gated_delta_kernel(const DeltaParams p) {
+// exp(rate * softplus(x)), rate < 0: exact library functions in 32-bit storage; in bfloat16 storage the fast
+// intrinsics (a few units in the last place of a float, far below what the rounding of q, k and v to bfloat16
+// leaves), which cost a tenth of the instructions: a producer warp computes one of these per token, head and
+// key channel
+template <typename T> __device__ __forceinline__ float decay_of(float rate, float x);
+template <> __device__ __forceinline__ float decay_of<float>(float rate, float x) { return expf(rate * softplus_f(x)); }
+template <> __device__ __forceinline__ float decay_of<bf16>(float rate, float x) {
+  return __expf(rate * (x > 20.f ? x : __logf(1.f + __expf(x))));
+}
+
+// PW producer warps: 4 for walks over many tokens; 1 for steps of a few tokens a sequence (decoding), where a
+// CTA lives for microseconds and what counts is how many of them fit an SM
+template <typename T, int R, int KS, bool CH, int PW>
+__global__ void __launch_bounds__(PW == 1 ? 288 : 384, PW == 1 ? 3 : 1) gated_delta_kernel(const DeltaParams p) {
   extern __shared__ __align__(16) float sm[];
-  constexpr int DKP = R * KS;  // rows a column's threads cover; rows >= dk hold k = q = 0
+  constexpr int RP = R + 4;      // a thread's rows in shared memory, padded so that the KS lanes of a column hit other banks
+  constexpr int DKS = KS * RP;   // floats of one k, q or g vector in shared memory
+  constexpr int DKP = R * KS;    // rows a column's threads cover; rows >= dk hold k = q = 0
+  constexpr int DPL = (DKP + 31) / 32;  // elements of a vector per producer lane
+  constexpr int JB = DPL <= 4 ? 4 : (DPL <= 8 ? 2 : 1);  // tokens a producer warp loads at once
   const int b = blockIdx.x, h = blockIdx.y;
   const int first = p.qsl[b], q_len = p.qsl[b + 1] - first;
   const int slot = p.state_slots[b];
   if (q_len <= 0 || slot < 0) return;
-  const int cols = blockDim.x / KS;
-  const int ks = threadIdx.x % KS, cl = threadIdx.x / KS;
-  const int col = blockIdx.z * cols + cl;
-  const bool live = col < p.dv;
-  const int kvh = h / (p.H / p.G);
+  const int CT = blockDim.x - PW * 32;  // consumer threads
+  const int cols = CT / KS;
   const int dk = p.dk, dv = p.dv, TB = p.chunk;
-  float* ks_s = sm;                  // [TB][DKP] unit keys
-  float* qs_s = ks_s + TB * DKP;     // [TB][DKP] unit queries, scaled
-  float* gs_s = qs_s + TB * DKP;     // [TB][DKP] decay per row (per_channel) or [TB] (one a head)
-  float* vs_s = gs_s + (p.per_channel ? TB * DKP : TB);  // [TB][cols]
-  float* bs_s = vs_s + TB * cols;    // [TB]
-
-  float S[R];
+  const int kvh = h / (p.H / p.G);
+  const bool producer = threadIdx.x >= CT;
+  // layout of a chunk buffer: k [TB][DKS], q [TB][DKS], (g [TB][DKS],) v [TB][cols], beta [TB], k.q [TB], g of the head [TB]
+  const int off_q = TB * DKS, off_g = 2 * TB * DKS, off_v = (CH ? 3 : 2) * TB * DKS;
+  const int off_beta = off_v + TB * cols, off_kq = off_beta + TB, off_gh = off_kq + TB;
   float* sg = p.state + (size_t)slot * p.state_stride + (size_t)h * dk * dv;
-#pragma unroll
-  for (int i = 0; i < R; ++i) {
-    const int r = i * KS + ks;
-    S[i] = (live && r < dk) ? sg[(size_t)r * dv + col] : 0.f;
-  }
-  const T* qg = (const T*)p.q;
-  const T* kg = (const T*)p.k;
-  const T* vg = (const T*)p.v;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-  const float neg_rate = -expf(p.A_log[h]);
+  const int col0 = blockIdx.z * cols;
+  const int nchunks = (q_len + TB - 1) / TB;
 
-  for (int t0 = 0; t0 < q_len; t0 += TB) {
-    const int nt = min(TB, q_len - t0);
-    __syncthreads();  // the chunk before has been walked
-    // ---- prepare the chunk: a warp per token
-    for (int tt = warp; tt < nt; tt += nwarps) {
-      const size_t n = (size_t)(first + t0 + tt);
-      const T* kr = kg + n * p.qkv_stride + (size_t)kvh * dk;
-      const T* qr = qg + n * p.qkv_stride + (size_t)kvh * dk;
-      float sk = 0.f, sq = 0.f;
-      for (int r = lane; r < dk; r += 32) {
-        const float kv = to_float<T>(kr[r]), qv = to_float<T>(qr[r]);
-        sk = fmaf(kv, kv, sk);
-        sq = fmaf(qv, qv, sq);
-      }
-      sk = warp_sum(sk);
-      sq = warp_sum(sq);
-      const float ik = 1.f / sqrtf(sk + p.norm_eps), iq = p.q_scale / sqrtf(sq + p.norm_eps);
-      for (int r = lane; r < DKP; r += 32) {
-        ks_s[tt * DKP + r] = r < dk ? to_float<T>(kr[r]) * ik : 0.f;
-        qs_s[tt * DKP + r] = r < dk ? to_float<T>(qr[r]) * iq : 0.f;
-      }
-      if (p.per_channel) {
-        const float* ar = p.a + n * p.a_stride + (size_t)h * dk;
-        const float* br = p.dt_bias + (size_t)h * dk;
-        for (int r = lane; r < DKP; r += 32) gs_s[tt * DKP + r] = r < dk ? expf(neg_rate * softplus_f(ar[r] + br[r])) : 1.f;
-      } else if (lane == 0) {
-        gs_s[tt] = expf(neg_rate * softplus_f(p.a[n * p.a_stride + h] + p.dt_bias[h]));
-      }
-      if (lane == 0) bs_s[tt] = sigmoid_f(p.b[n * p.b_stride + h]);
+  // ---- producers: chunk c into buffer `buf`.  Every global load of a warp's tokens is issued before the first
+  // of them is used (a load that is waited for alone costs most of a microsecond, and there would be a dozen per
+  // chunk); what does not change from token to token is loaded once.
+  const int pt = threadIdx.x - CT, pwarp = pt >> 5, plane = pt & 31;
+  float bias[DPL];
+  float neg_rate = 0.f, bias_h = 0.f;
+  if (producer) {
+    neg_rate = -expf(p.A_log[h]);
+    if (!CH) bias_h = p.dt_bias[h];
+#pragma unroll
+    for (int e = 0; e < DPL; ++e) {
+      const int r = plane + 32 * e;
+      bias[e] = (CH && r < dk) ? p.dt_bias[(size_t)h * dk + r] : 0.f;
     }
-    for (int idx = threadIdx.x; idx < nt * cols; idx += blockDim.x) {
-      const int tt = idx / cols, c = idx - tt * cols;
-      const int cc = blockIdx.z * cols + c;
-      vs_s[idx] = cc < dv ? to_float<T>(vg[(size_t)(first + t0 + tt) * p.qkv_stride + (size_t)h * dv + cc]) : 0.f;
+  }
+  auto prepare = [&](int c, float* buf) {
+    const int warp = pwarp, lane = plane;
+    const int t0 = c * TB, nt = min(TB, q_len - t0);
+    const T* qg = (const T*)p.q;
+    const T* kg = (const T*)p.k;
+    const T* vg = (const T*)p.v;
+    for (int j0 = 0; j0 * PW < TB; j0 += JB) {
+      float kv[JB][DPL], qv[JB][DPL], av[JB][DPL], bl[JB], al[JB];
+#pragma unroll
+      for (int j = 0; j < JB; ++j) {
+        const int tt = warp + (j0 + j) * PW;
+        const size_t n = (size_t)(first + t0 + (tt < nt ? tt : 0));
+        const T* kr = kg + n * p.qkv_stride + (size_t)kvh * dk;
+        const T* qr = qg + n * p.qkv_stride + (size_t)kvh * dk;
+        const float* ar = p.a + n * p.a_stride + (size_t)h * dk;
+#pragma unroll
+        for (int e = 0; e < DPL; ++e) {
+          const int r = lane + 32 * e;
+          const bool ok = r < dk && tt < nt;
+          kv[j][e] = ok ? to_float<T>(kr[r]) : 0.f;
+          qv[j][e] = ok ? to_float<T>(qr[r]) : 0.f;
+          if (CH) av[j][e] = ok ? ar[r] : 0.f;
+        }
+        bl[j] = p.b[n * p.b_stride + h];
+        al[j] = CH ? 0.f : p.a[n * p.a_stride + h];
+      }
+      // this CTA's columns of v: a thread's elements of the chunk, loaded together
+      constexpr int VPT = 4;
+      for (int base = 0; base < nt * cols && j0 == 0; base += VPT * PW * 32) {
+        float vv[VPT];
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+          const int idx = base + i * PW * 32 + pt;
+          const int tt = idx / cols, cc = col0 + (idx - tt * cols);
+          vv[i] = (idx < nt * cols && cc < dv) ? to_float<T>(vg[(size_t)(first + t0 + tt) * p.qkv_stride + (size_t)h * dv + cc]) : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+          const int idx = base + i * PW * 32 + pt;
+          if (idx < nt * cols) buf[off_v + idx] = vv[i];
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < JB; ++j) {
+        const int tt = warp + (j0 + j) * PW;
+        if (tt >= nt) continue;  // warp-uniform
+        float sk = 0.f, sq = 0.f, kq = 0.f;
+#pragma unroll
+        for (int e = 0; e < DPL; ++e) {
+          sk = fmaf(kv[j][e], kv[j][e], sk);
+          sq = fmaf(qv[j][e], qv[j][e], sq);
+          kq = fmaf(kv[j][e], qv[j][e], kq);
+        }
+        sk = warp_sum(sk);
+        sq = warp_sum(sq);
+        kq = warp_sum(kq);
+        const float ik = 1.f / sqrtf(sk + p.norm_eps), iq = p.q_scale / sqrtf(sq + p.norm_eps);
+#pragma unroll
+        for (int e = 0; e < DPL; ++e) {
+          const int r = lane + 32 * e;
+          if (r < DKP) {
+            const int at = tt * DKS + (r / R) * RP + (r % R);
+            buf[at] = kv[j][e] * ik;
+            buf[off_q + at] = qv[j][e] * iq;
+            if (CH) buf[off_g + at] = r < dk ? decay_of<T>(neg_rate, av[j][e] + bias[e]) : 1.f;
+          }
+        }
+        if (lane == 0) {
+          buf[off_beta + tt] = sigmoid_f(bl[j]);
+          buf[off_kq + tt] = kq * ik * iq;
+          if (!CH) buf[off_gh + tt] = decay_of<T>(neg_rate, al[j] + bias_h);
+        }
+      }
+    }
+  };
+
+  float* buf0 = sm;
+  float* buf1 = sm + p.buf_floats;
+  const int ks = threadIdx.x % KS, cl = threadIdx.x / KS;
+  const int col = col0 + cl;
+  const bool live = !producer && col < dv;
+  float S[R];
+  if (producer) {
+    prepare(0, buf0);
+  } else {
+    // the state's tile [dk][cols] through shared memory (it borrows the second buffer, which is filled only later)
+    float* stage = buf1;
+    for (int idx = threadIdx.x; idx < dk * cols; idx += CT) {
+      const int r = idx / cols, c = idx - r * cols;
+      stage[r * (cols + 1) + c] = (col0 + c < dv) ? sg[(size_t)r * dv + col0 + c] : 0.f;
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(CT) : "memory");
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      const int r = ks * R + i;
+      S[i] = r < dk ? stage[r * (cols + 1) + cl] : 0.f;
+    }
+  }
+  __syncthreads();
+
+  for (int c = 0; c < nchunks; ++c) {
+    float* buf = (c & 1) ? buf1 : buf0;
+    if (producer) {
+      if (c + 1 < nchunks) prepare(c + 1, (c & 1) ? buf0 : buf1);
+    } else {
+      const int t0 = c * TB, nt = min(TB, q_len - t0);
+      // the vectors of a token are fetched into registers while the token before is still in its shuffles
+      float4 kn[R / 4], qn[R / 4], gn[R / 4];
+      auto fetch = [&](int tt) {
+        const float4* k4 = reinterpret_cast<const float4*>(buf + tt * DKS + ks * RP);
+        const float4* q4 = reinterpret_cast<const float4*>(buf + off_q + tt * DKS + ks * RP);
+        const float4* g4 = reinterpret_cast<const float4*>(buf + off_g + tt * DKS + ks * RP);
+#pragma unroll
+        for (int i = 0; i < R / 4; ++i) {
+          kn[i] = k4[i];
+          qn[i] = q4[i];
+          if (CH) gn[i] = g4[i];
+        }
+      };
+      fetch(0);
+      for (int tt = 0; tt < nt; ++tt) {
+        const float gh = CH ? 1.f : buf[off_gh + tt];
+        const float beta = buf[off_beta + tt], vv = buf[off_v + tt * cols + cl], kq = buf[off_kq + tt];
+        float kr[R];
+        float dk_[4] = {0.f, 0.f, 0.f, 0.f}, dq_[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int i = 0; i < R / 4; ++i) {
+          const float4 kk = kn[i], qq = qn[i];
+          float4 gg = make_float4(gh, gh, gh, gh);
+          if (CH) gg = gn[i];
+          kr[4 * i] = kk.x; kr[4 * i + 1] = kk.y; kr[4 * i + 2] = kk.z; kr[4 * i + 3] = kk.w;
+          S[4 * i] *= gg.x; S[4 * i + 1] *= gg.y; S[4 * i + 2] *= gg.z; S[4 * i + 3] *= gg.w;
+          dk_[0] = fmaf(S[4 * i], kk.x, dk_[0]); dk_[1] = fmaf(S[4 * i + 1], kk.y, dk_[1]);
+          dk_[2] = fmaf(S[4 * i + 2], kk.z, dk_[2]); dk_[3] = fmaf(S[4 * i + 3], kk.w, dk_[3]);
+          dq_[0] = fmaf(S[4 * i], qq.x, dq_[0]); dq_[1] = fmaf(S[4 * i + 1], qq.y, dq_[1]);
+          dq_[2] = fmaf(S[4 * i + 2], qq.z, dq_[2]); dq_[3] = fmaf(S[4 * i + 3], qq.w, dq_[3]);
+        }
+        if (tt + 1 < nt) fetch(tt + 1);
+        float dotk = (dk_[0] + dk_[1]) + (dk_[2] + dk_[3]);
+        float dotq = (dq_[0] + dq_[1]) + (dq_[2] + dq_[3]);
+#pragma unroll
+        for (int o = KS >> 1; o > 0; o >>= 1) {
+          dotk += __shfl_xor_sync(0xffffffffu, dotk, o);
+          dotq += __shfl_xor_sync(0xffffffffu, dotq, o);
+        }
+        const float u = beta * (vv - dotk);
+#pragma unroll
+        for (int i = 0; i < R; ++i) S[i] = fmaf(kr[i], u, S[i]);
+        if (ks == 0 && live) p.out[(size_t)(first + t0 + tt) * p.out_stride + (size_t)h * dv + col] = fmaf(u, kq, dotq);
+      }
     }
     __syncthreads();
-    // ---- walk the chunk
-    for (int tt = 0; tt < nt; ++tt) {
-      const float* kk = ks_s + tt * DKP + ks;
-      const float* qq = qs_s + tt * DKP + ks;
-      float dot = 0.f;
-      if (p.per_channel) {
-        const float* gg = gs_s + tt * DKP + ks;
-#pragma unroll
-        for (int i = 0; i < R; ++i) {
-          S[i] *= gg[i * KS];
-          dot = fmaf(S[i], kk[i * KS], dot);
-        }
-      } else {
-        const float g = gs_s[tt];
-#pragma unroll
-        for (int i = 0; i < R; ++i) {
-          S[i] *= g;
-          dot = fmaf(S[i], kk[i * KS], dot);
-        }
-      }
-#pragma unroll
-      for (int o = KS >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-      const float u = bs_s[tt] * (vs_s[tt * cols + cl] - dot);
-      float ro = 0.f;
-#pragma unroll
-      for (int i = 0; i < R; ++i) {
-        S[i] = fmaf(kk[i * KS], u, S[i]);
-        ro = fmaf(S[i], qq[i * KS], ro);
-      }
-#pragma unroll
-      for (int o = KS >> 1; o > 0; o >>= 1) ro += __shfl_xor_sync(0xffffffffu, ro, o);
-      if (ks == 0 && live) p.out[(size_t)(first + t0 + tt) * p.out_stride + (size_t)h * dv + col] = ro;
-    }
   }
+  if (!producer) {
+    float* stage = buf0;  // both buffers are free now
 #pragma unroll
-  for (int i = 0; i < R; ++i) {
-    const int r = i * KS + ks;
-    if (live && r < dk) sg[(size_t)r * dv + col] = S[i];
+    for (int i = 0; i < R; ++i) {
+      const int r = ks * R + i;
+      if (r < dk) stage[r * (cols + 1) + cl] = S[i];
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(CT) : "memory");
+    for (int idx = threadIdx.x; idx < dk * cols; idx += CT) {
+      const int r = idx / cols, c = idx - r * cols;
+      if (col0 + c < dv) sg[(size_t)r * dv + col0 + c] = stage[r * (cols + 1) + c];
+    }
   }
 }
 
-template <typename T, int R, int KS>
+template <typename T, int R, int KS, bool CH, int PW>
 int launch_delta(DeltaParams p, int B, cudaStream_t st) {
-  constexpr int DKP = R * KS;
-  int threads = (p.dv * KS + 31) / 32 * 32;
-  const int cap = R * KS > 512 ? 1024 : 256;
-  if (threads > cap) threads = cap;
-  if (threads < KS) threads = KS;
-  const int cols = threads / KS;
-  // a chunk's k, q, (g,) v and beta within 48 KB of shared memory
-  const int per_token = (2 + (p.per_channel ? 1 : 0)) * DKP + cols + 2;
-  int chunk = (46 * 1024 / 4) / per_token;
-  if (chunk > 16) chunk = 16;
-  if (chunk < 1) return (int)cudaErrorInvalidValue;
+  constexpr int RP = R + 4, DKS = KS * RP;
+  // consumer threads: steps of few tokens take 256 (fewer CTAs, each a short life); walks take 128 while that
+  // leaves SMs free (a link of the chain is no faster with more columns in a CTA, and small CTAs spread over
+  // more SMs), else 256
+  int ct = PW == 1 ? 256 : 128;
+  if (ct < KS) ct = KS;
+  if (PW != 1) {
+    const int cols128 = ct / KS;
+    const long long ctas = (long long)B * p.H * ((p.dv + cols128 - 1) / cols128);
+    if (ctas > 2 * 148 && 256 / KS <= p.dv) ct = 256;
+  }
+  while (ct > 32 && ct > KS && (ct / 2) / KS >= p.dv) ct /= 2;  // no more columns than the head has
+  const int cols = ct / KS;
+  const int per_token = (CH ? 3 : 2) * DKS + cols + 3;
+  int chunk = PW == 1 ? 4 : 16;
+  while (chunk > PW && (size_t)2 * chunk * per_token * sizeof(float) > 96 * 1024) chunk -= PW;
+  int buf_floats = (chunk * per_token + 3) / 4 * 4;
+  const int stage = p.dk * (cols + 1);
+  if (buf_floats < stage) buf_floats = (stage + 3) / 4 * 4;
+  const size_t smem = (size_t)2 * buf_floats * sizeof(float);
+  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
   p.chunk = chunk;
-  const size_t smem = (size_t)chunk * per_token * sizeof(float);
+  p.buf_floats = buf_floats;
+  auto kern = gated_delta_kernel<T, R, KS, CH, PW>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
   dim3 grid(B, p.H, (p.dv + cols - 1) / cols);
-  gated_delta_kernel<T, R, KS><<<grid, threads, smem, st>>>(p);
+  kern<<<grid, ct + PW * 32, smem, st>>>(p);
   return KVF_LAUNCH_STATUS();
 }
 
-template <typename T>
-int dispatch_delta(const DeltaParams& p, int B, cudaStream_t st) {
-  if (p.dk <= 16) return launch_delta<T, 16, 1>(p, B, st);
-  if (p.dk <= 32) return launch_delta<T, 16, 2>(p, B, st);
-  if (p.dk <= 64) return launch_delta<T, 16, 4>(p, B, st);
-  if (p.dk <= 128) return launch_delta<T, 16, 8>(p, B, st);
-  if (p.dk <= 256) return launch_delta<T, 16, 16>(p, B, st);
-  if (p.dk <= 512) return launch_delta<T, 32, 16>(p, B, st);
-  if (p.dk <= 1024) return launch_delta<T, 32, 32>(p, B, st);
+// Rows a thread: 16 for steps of few tokens; for walks 8 where the head is wide enough and the step has so few
+// (sequence, head) pairs that the finer split still fits the device at once (twice the warps, each with half
+// the chain of a token), else 16.
+template <typename T, bool CH, int PW>
+int dispatch_delta_rows(const DeltaParams& p, int B, cudaStream_t st) {
+  const int dk = p.dk;
+  if (PW != 1 && dk > 16 && dk <= 256) {
+    const long long warps8 = (long long)B * p.H * p.dv * ((dk + 7) / 8) / 32;
+    if (warps8 <= 4 * 592) {
+      if (dk <= 32) return launch_delta<T, 8, 4, CH, PW>(p, B, st);
+      if (dk <= 64) return launch_delta<T, 8, 8, CH, PW>(p, B, st);
+      if (dk <= 128) return launch_delta<T, 8, 16, CH, PW>(p, B, st);
+      return launch_delta<T, 8, 32, CH, PW>(p, B, st);
+    }
+  }
+  if (dk <= 16) return launch_delta<T, 16, 1, CH, PW>(p, B, st);
+  if (dk <= 32) return launch_delta<T, 16, 2, CH, PW>(p, B, st);
+  if (dk <= 64) return launch_delta<T, 16, 4, CH, PW>(p, B, st);
+  if (dk <= 128) return launch_delta<T, 16, 8, CH, PW>(p, B, st);
+  if (dk <= 256) return launch_delta<T, 16, 16, CH, PW>(p, B, st);
+  if (dk <= 512) return launch_delta<T, 32, 16, CH, PW>(p, B, st);
+  if (dk <= 1024) return launch_delta<T, 32, 32, CH, PW>(p, B, st);
   return (int)cudaErrorInvalidValue;
+}
+
+template <typename T>
+int dispatch_delta(const DeltaParams& p, int B, int max_q_len, cudaStream_t st) {
+  const bool few = max_q_len > 0 && max_q_len <= 4;
+  if (p.per_channel) return few ? dispatch_delta_rows<T, true, 1>(p, B, st) : dispatch_delta_rows<T, true, 4>(p, B, st);
+  return few ? dispatch_delta_rows<T, false, 1>(p, B, st) : dispatch_delta_rows<T, false, 4>(p, B, st);
 }
 
 // ---------------------------------------------------------------- gated RMS norm of a head's read-out
@@ -298,11 +522,15 @@ __global__ void __launch_bounds__(128) gated_head_norm_kernel(const float* __res
                                     void* out, int out_stride, cudaStream_t st) {                                      \
     if (N <= 0 || B <= 0 || C <= 0) return 0;                                                                          \
     if (taps <= 0 || (unsigned)B > 65535u) return (int)cudaErrorInvalidValue;                                          \
+    constexpr int V = ConvVec<T>::N;                                                                                   \
+    const bool vec = C % V == 0 && x_stride % V == 0 && out_stride % V == 0 && ((uintptr_t)x % 16) == 0 &&             \
+                     ((uintptr_t)out % 16) == 0;                                                                       \
+    int rc = vec ? launch_conv<T, V>((const T*)x, x_stride, w, state, state_stride, qsl, state_slots, N, B, C, taps,   \
+                                     act, (T*)out, out_stride, st)                                                     \
+                 : launch_conv<T, 1>((const T*)x, x_stride, w, state, state_stride, qsl, state_slots, N, B, C, taps,   \
+                                     act, (T*)out, out_stride, st);                                                    \
     int gy = (C + 255) / 256;                                                                                          \
     if (gy > 65535) gy = 65535;                                                                                        \
-    causal_conv_kernel<T><<<dim3(N, gy), 256, 0, st>>>((const T*)x, x_stride, w, state, state_stride, qsl,             \
-                                                       state_slots, B, C, taps, act, (T*)out, out_stride);             \
-    int rc = KVF_LAUNCH_STATUS();                                                                                      \
     if (rc || taps == 1) return rc;                                                                                    \
     conv_state_kernel<T><<<dim3(B, gy), 256, 0, st>>>((const T*)x, x_stride, state, state_stride, qsl, state_slots,    \
                                                       C, taps);                                                        \
@@ -312,15 +540,16 @@ __global__ void __launch_bounds__(128) gated_head_norm_kernel(const float* __res
                                     int b_stride, const float* a, int a_stride, const float* A_log,                    \
                                     const float* dt_bias, int per_channel, float* state, long long state_stride,       \
                                     float* out, int out_stride, const int* qsl, const int* state_slots, int B, int H,  \
-                                    int G, int dk, int dv, float q_scale, float norm_eps, cudaStream_t st) {           \
+                                    int G, int dk, int dv, float q_scale, float norm_eps, int max_q_len,               \
+                                    cudaStream_t st) {                                                                 \
     if (B <= 0) return 0;                                                                                              \
     if (H <= 0 || G <= 0 || H % G || dk <= 0 || dv <= 0 || (unsigned)H > 65535u) return (int)cudaErrorInvalidValue;    \
     DeltaParams p;                                                                                                     \
     p.q = q; p.k = k; p.v = v; p.qkv_stride = qkv_stride; p.b = b; p.b_stride = b_stride; p.a = a;                     \
     p.a_stride = a_stride; p.A_log = A_log; p.dt_bias = dt_bias; p.per_channel = per_channel; p.state = state;         \
     p.state_stride = state_stride; p.out = out; p.out_stride = out_stride; p.qsl = qsl; p.state_slots = state_slots;   \
-    p.H = H; p.G = G; p.dk = dk; p.dv = dv; p.q_scale = q_scale; p.norm_eps = norm_eps; p.chunk = 1;                    \
-    return dispatch_delta<T>(p, B, st);                                                                                \
+    p.H = H; p.G = G; p.dk = dk; p.dv = dv; p.q_scale = q_scale; p.norm_eps = norm_eps; p.chunk = 1; p.buf_floats = 0;  \
+    return dispatch_delta<T>(p, B, max_q_len, st);                                                                     \
   }                                                                                                                    \
   KVF_API int kvf_gated_head_norm_##SUF(const float* o, int o_stride, const void* gate, int gate_stride,               \
                                         const float* w, float eps, int act, long long N, int H, int dv, void* out,     \

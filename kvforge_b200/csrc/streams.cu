@@ -89,6 +89,76 @@ __global__ void __launch_bounds__(256) hc_step_kernel(const HcParams p, int S_rt
   for (int c = threadIdx.x; c < W; c += blockDim.x) o[c] = from_float<T>(urow[c] * inv * p.norm_w[c]);
 }
 
+// The same with a row's columns spread over the CTA so that a thread owns at most CPT of them and every load of
+// the row (streams, pending result or its slices) is in flight before the first is used; the read-out stays in
+// registers between the sum of squares and the write.  For widths up to 1024 * CPT.
+template <typename T, int SC, int CPT>
+__global__ void __launch_bounds__(1024) hc_step_rows_kernel(const HcParams p) {
+  __shared__ float red[32];
+  __shared__ float s_mix[SC * SC], s_out[SC], s_in[SC];
+  const int r = blockIdx.x;
+  const size_t n = p.rows ? (size_t)p.rows[r] : (size_t)r;
+  const int W = p.W;
+  if (threadIdx.x < SC * SC && p.mix) s_mix[threadIdx.x] = p.mix[threadIdx.x];
+  if (threadIdx.x < SC) {
+    s_out[threadIdx.x] = p.mix ? p.out_w[threadIdx.x] : 0.f;
+    s_in[threadIdx.x] = p.in_w ? p.in_w[threadIdx.x] : 1.f;
+  }
+  float* xs = p.streams + n * (size_t)SC * W;
+  const T* yr = p.y ? (const T*)p.y + n * W : nullptr;
+  const float* pr = p.partials ? p.partials + n * W : nullptr;
+  float x[CPT][SC], y[CPT], nw[CPT];
+#pragma unroll
+  for (int k = 0; k < CPT; ++k) {
+    const int c = threadIdx.x + k * blockDim.x;
+#pragma unroll
+    for (int s = 0; s < SC; ++s) x[k][s] = c < W ? xs[(size_t)s * W + c] : 0.f;
+    y[k] = (yr && c < W) ? to_float<T>(yr[c]) : 0.f;
+    nw[k] = c < W ? p.norm_w[c] : 0.f;
+  }
+  if (pr) {
+    for (int sl = 0; sl < p.nsplit; ++sl) {
+#pragma unroll
+      for (int k = 0; k < CPT; ++k) {
+        const int c = threadIdx.x + k * blockDim.x;
+        if (c < W) y[k] += pr[(size_t)sl * p.split_stride + c];
+      }
+    }
+  }
+  __syncthreads();
+  float u[CPT];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < CPT; ++k) {
+    const int c = threadIdx.x + k * blockDim.x;
+    float uu = 0.f;
+    if (p.mix) {
+#pragma unroll
+      for (int t = 0; t < SC; ++t) {
+        float acc = 0.f;
+#pragma unroll
+        for (int s = 0; s < SC; ++s) acc = fmaf(s_mix[s * SC + t], x[k][s], acc);
+        acc = fmaf(s_out[t], y[k], acc);
+        if (!p.rows && c < W) xs[(size_t)t * W + c] = acc;
+        uu = fmaf(s_in[t], acc, uu);
+      }
+    } else {
+#pragma unroll
+      for (int t = 0; t < SC; ++t) uu = fmaf(s_in[t], x[k][t], uu);
+    }
+    u[k] = uu;
+    ss = fmaf(uu, uu, ss);
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.f / sqrtf(ss / (float)W + p.eps);
+  T* o = (T*)p.out + (size_t)r * W;
+#pragma unroll
+  for (int k = 0; k < CPT; ++k) {
+    const int c = threadIdx.x + k * blockDim.x;
+    if (c < W) o[c] = from_float<T>(u[k] * inv * nw[k]);
+  }
+}
+
 // every stream starts as the embedding's output
 __global__ void replicate_kernel(const float* __restrict__ src, float* __restrict__ streams, int S, int W, size_t total) {
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -112,6 +182,52 @@ struct BranchParams {
   float eps;
   void* out;
 };
+
+// A thread owns at most CPT columns of a row and keeps them in registers for every branch; all loads first.
+template <typename T, int CPT>
+__global__ void __launch_bounds__(1024) branch_norm_mean_rows_kernel(const BranchParams p) {
+  __shared__ float red[32];
+  const size_t n = blockIdx.x;
+  const int W = p.W;
+  float v[MAX_BRANCHES][CPT];
+#pragma unroll
+  for (int b = 0; b < MAX_BRANCHES; ++b) {
+#pragma unroll
+    for (int k = 0; k < CPT; ++k) {
+      const int c = threadIdx.x + k * blockDim.x;
+      v[b][k] = 0.f;
+      if (b < p.nb && c < W) {
+        if (p.y[b]) v[b][k] = to_float<T>(((const T*)p.y[b])[n * W + c]);
+        else
+          for (int sl = 0; sl < p.nsplit[b]; ++sl) v[b][k] += p.partials[b][n * W + (size_t)sl * p.split_stride[b] + c];
+      }
+    }
+  }
+  float inv[MAX_BRANCHES];
+#pragma unroll
+  for (int b = 0; b < MAX_BRANCHES; ++b) {
+    inv[b] = 0.f;
+    if (b < p.nb) {  // uniform over the CTA
+      float ss = 0.f;
+#pragma unroll
+      for (int k = 0; k < CPT; ++k) ss = fmaf(v[b][k], v[b][k], ss);
+      ss = block_sum(ss, red);
+      inv[b] = 1.f / sqrtf(ss / (float)W + p.eps);
+    }
+  }
+  const float share = 1.f / (float)p.nb;
+  T* o = (T*)p.out + n * W;
+#pragma unroll
+  for (int k = 0; k < CPT; ++k) {
+    const int c = threadIdx.x + k * blockDim.x;
+    if (c >= W) continue;
+    float acc = 0.f;
+#pragma unroll
+    for (int b = 0; b < MAX_BRANCHES; ++b)
+      if (b < p.nb) acc += v[b][k] * inv[b] * p.w[b][c];
+    o[c] = from_float<T>(acc * share);
+  }
+}
 
 template <typename T>
 __global__ void __launch_bounds__(256) branch_norm_mean_kernel(const BranchParams p) {
@@ -203,8 +319,23 @@ __global__ void __launch_bounds__(256) rope_cache_general_kernel(T* __restrict__
   }
 }
 
+static inline int row_threads(int W, int cpt) {
+  int t = ((W + cpt - 1) / cpt + 31) / 32 * 32;
+  return t > 1024 ? 1024 : t;
+}
+
 template <typename T, int SC>
 int launch_hc(const HcParams& p, int n_rows, int S, cudaStream_t st) {
+  if constexpr (SC > 0) {
+   if (p.W <= 8192) {
+    const dim3 g(n_rows);
+    if (p.W <= 1024) hc_step_rows_kernel<T, SC, 1><<<g, row_threads(p.W, 1), 0, st>>>(p);
+    else if (p.W <= 2048) hc_step_rows_kernel<T, SC, 2><<<g, row_threads(p.W, 2), 0, st>>>(p);
+    else if (p.W <= 4096) hc_step_rows_kernel<T, SC, 4><<<g, row_threads(p.W, 4), 0, st>>>(p);
+    else hc_step_rows_kernel<T, SC, 8><<<g, row_threads(p.W, 8), 0, st>>>(p);
+    return KVF_LAUNCH_STATUS();
+   }
+  }
   hc_step_kernel<T, SC><<<dim3(n_rows), 256, (size_t)p.W * sizeof(float), st>>>(p, S);
   return KVF_LAUNCH_STATUS();
 }
@@ -243,6 +374,14 @@ int launch_hc(const HcParams& p, int n_rows, int S, cudaStream_t st) {
       if (!p.y[b] && !p.partials[b]) return (int)cudaErrorInvalidValue;                                                \
     }                                                                                                                  \
     p.nb = nb; p.W = W; p.eps = eps; p.out = out;                                                                      \
+    if (W <= 8192) {                                                                                                   \
+      const dim3 g((unsigned)N);                                                                                       \
+      if (W <= 1024) branch_norm_mean_rows_kernel<T, 1><<<g, row_threads(W, 1), 0, st>>>(p);                           \
+      else if (W <= 2048) branch_norm_mean_rows_kernel<T, 2><<<g, row_threads(W, 2), 0, st>>>(p);                      \
+      else if (W <= 4096) branch_norm_mean_rows_kernel<T, 4><<<g, row_threads(W, 4), 0, st>>>(p);                      \
+      else branch_norm_mean_rows_kernel<T, 8><<<g, row_threads(W, 8), 0, st>>>(p);                                     \
+      return KVF_LAUNCH_STATUS();                                                                                      \
+    }                                                                                                                  \
     const size_t smem = (size_t)nb * W * sizeof(float);                                                                \
     if (smem > 48 * 1024) {                                                                                            \
       cudaError_t e = cudaFuncSetAttribute(branch_norm_mean_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,    \

@@ -37,7 +37,7 @@ _SIGNATURES = {
     "kvf_argmax_f32": "pliipipp",
     # library "mixers"
     "kvf_causal_conv_{s}": "pipplppiiiiipip",
-    "kvf_gated_delta_{s}": "pppipipippiplpippiiiiiffp",
+    "kvf_gated_delta_{s}": "pppipipippiplpippiiiiiffip",
     "kvf_gated_head_norm_{s}": "pipipfiliipip",
     "kvf_hc_step_{s}": "pppilppppppiiifp",
     "kvf_branch_norm_mean_{s}": "pppppilifpp",
@@ -965,7 +965,7 @@ def gated_delta(
     q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta_logits: torch.Tensor, step_logits: torch.Tensor,
     a_log: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor, out: torch.Tensor, qsl: torch.Tensor,
     state_slots: torch.Tensor, num_seqs: int, num_heads: int, num_kv_heads: int, dk: int, dv: int, q_scale: float,
-    norm_eps: float = 1e-6,
+    norm_eps: float = 1e-6, max_query_len: int = 0,
 ) -> None:  # fmt: skip
     """The gated delta rule over a flat batch, token by token per sequence, on the state
     ``S [heads, dk, dv]`` of each sequence's slot (``csrc/sequence_mix.cu`` has the equations).
@@ -973,7 +973,8 @@ def gated_delta(
     ``q, k [N, G*dk]`` and ``v [N, H*dv]`` are column slices of one buffer (same row stride);
     ``beta_logits`` float ``[N, H]``; ``step_logits`` float ``[N, H]`` (one decay a head) or
     ``[N, H*dk]`` (one a key channel), with ``dt_bias`` of the same width and ``a_log [H]``;
-    ``out`` float ``[N, H*dv]`` gets the read-out."""
+    ``out`` float ``[N, H*dv]`` gets the read-out.  ``max_query_len`` (0 = unknown): the most rows any
+    sequence of the step brings; up to 4 the kernel takes the form made for steps of single tokens."""
     s = _suffix(q.dtype)
     h, g = int(num_heads), int(num_kv_heads)
     for t, w, what in ((q, g * dk, "q"), (k, g * dk, "k"), (v, h * dv, "v")):
@@ -999,7 +1000,7 @@ def gated_delta(
         _fn(name, MIXERS_LIB)(
             _ptr(q), _ptr(k), _ptr(v), q.stride(0), _ptr(beta_logits), beta_logits.stride(0), _ptr(step_logits),
             step_logits.stride(0), _ptr(a_log), _ptr(dt_bias), 1 if per_channel else 0, sptr, sstride, _ptr(out),
-            out.stride(0), _ptr(qsl), _ptr(state_slots), num_seqs, h, g, dk, dv, float(q_scale), float(norm_eps), _stream(),
+            out.stride(0), _ptr(qsl), _ptr(state_slots), num_seqs, h, g, dk, dv, float(q_scale), float(norm_eps), int(max_query_len), _stream(),
         ),
         name,
     )  # fmt: skip

@@ -168,7 +168,7 @@ class GatedDeltaRule(Mixer):
         ops.gated_delta(
             qkv[:, : self.c_q], qkv[:, self.c_q : 2 * self.c_q], qkv[:, 2 * self.c_q :], small[:, :H], step, self.a_log, self.dt_bias,
             cache.state[:, self.conv_floats :], read, ctx.query_start_loc, ctx.state_slots, ctx.num_seqs, H, self.G, dk, dv,
-            q_scale=dk**-0.5, norm_eps=1e-6,
+            q_scale=dk**-0.5, norm_eps=1e-6, max_query_len=ctx.max_query_len,
         )  # fmt: skip
         y = rt.buf("delta.y", n, self.c_v)
         ops.gated_head_norm(read, gate, self.norm_w, self.eps, y, H, dv, activation=self.gate)
