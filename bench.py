@@ -600,10 +600,46 @@ def run_load(cfg, nreq: int, short_prompts: bool = False) -> dict:
             "tpot_p50_ms": round(m["tpot_p50_ms"], 3), "preemptions": stats["scheduler"]["num_preemptions"]}  # fmt: skip
 
 
+DESIGN_PAIRS = (("mopilorn-1b", "llama-3.2-1b"), ("mopilorn-3b", "llama-3.2-3b"))
+
+
+def run_designs(args) -> dict:
+    """Prompt and decode throughput of the Mopilorn shapes beside the Llama shapes of equal width, depth,
+    feed-forward and vocabulary (random weights): a prompt of 2,048 tokens, and decode steps of 8 and 64 requests
+    with 2,048 tokens behind them, each as captured graphs, timed on the device."""
+    import gc
+
+    import torch
+
+    from kvforge_b200 import PRESETS
+
+    out = {"only": "designs", "prompt_tokens": PREFILL_TOKENS, "decode_context": PROMPT_LEN, "shapes": {}}
+    steps, warmup = max(8, min(args.steps, 64)), max(3, args.warmup)
+    for pair in DESIGN_PAIRS:
+        for name in pair:
+            cfg = PRESETS[name]
+            row = {}
+            core = make_core(cfg, 64, PREFILL_TOKENS, PROMPT_LEN + steps + warmup + 32)
+            seconds = time_prefill(core, PREFILL_TOKENS, reps=3)
+            row["prefill_ms"] = round(1e3 * seconds, 3)
+            row["prefill_tokens_per_s"] = round(PREFILL_TOKENS / seconds, 1)
+            for batch in (8, 64):
+                sec, _, _ = time_decode(core, batch, [PROMPT_LEN + i for i in range(warmup + steps)], warmup)
+                row[f"decode_b{batch}_ms"] = round(1e3 * sec / steps, 4)
+                row[f"decode_b{batch}_tokens_per_s"] = round(batch * steps / sec, 1)
+            out["shapes"][name] = row
+            del core
+            gc.collect()
+            torch.cuda.empty_cache()
+    return out
+
+
 def run_only(args) -> dict:
     """One part alone on a small footing: what the profiler is pointed at."""
     from kvforge_b200 import PRESETS
 
+    if args.only == "designs":
+        return run_designs(args)
     cfg = PRESETS[args.preset]
     if args.only == "load":
         nreq = args.batch if args.batch != 8 else (256 if args.short_prompts else 64)
@@ -812,8 +848,8 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", choices=["own", "reference"], default="own")
-    ap.add_argument("--only", choices=["decode", "prefill", "mixed", "attention", "attention-prefill", "gemm", "sample", "load"], help="run one part alone and print a short line (for profiling)")
-    ap.add_argument("--preset", default="llama-3.2-1b", help="with --only: the shape (llama-3.2-1b, llama-3.2-3b, llama-3.1-8b)")
+    ap.add_argument("--only", choices=["decode", "prefill", "mixed", "attention", "attention-prefill", "gemm", "sample", "load", "designs"], help="run one part alone and print a short line (for profiling); 'designs': the Mopilorn shapes beside the Llama shapes of equal size")
+    ap.add_argument("--preset", default="llama-3.2-1b", help="with --only: the shape (llama-3.2-1b, llama-3.2-3b, llama-3.1-8b, mopilorn-1b, mopilorn-3b)")
     ap.add_argument("--split", type=int, default=0, help="with --only attention: keys per range (0 = the engine's choice)")
     ap.add_argument("--block-size", type=int, default=16, help="with --only attention / attention-prefill: tokens per page")
     ap.add_argument("--temperature", type=float, default=0.8, help="with --only sample (0 = greedy)")

@@ -69,6 +69,8 @@ __global__ void __launch_bounds__(128) causal_conv_kernel(const T* __restrict__ 
                                                           const int* __restrict__ qsl, const int* __restrict__ state_slots,
                                                           int N, int B, int C, int taps_rt, int act, T* __restrict__ out,
                                                           int out_stride, int rows) {
+  pdl_launch();
+  pdl_wait();
   const int taps = TAPS > 0 ? TAPS : taps_rt;
   const int c = (blockIdx.y * blockDim.x + threadIdx.x) * VEC;
   if (c >= C) return;
@@ -121,7 +123,7 @@ int launch_conv(const T* x, int x_stride, const float* w, const float* state, lo
   dim3 grid((N + rows - 1) / rows, (C + per_cta - 1) / per_cta);
   if (grid.y > 65535u) return (int)cudaErrorInvalidValue;
 #define KVF_CONV_CASE(TP)                                                                                             \
-  causal_conv_kernel<T, VEC, TP><<<grid, 128, 0, st>>>(x, x_stride, w, state, state_stride, qsl, state_slots, N, B, C, \
+  launch(causal_conv_kernel<T, VEC, TP>, dim3(grid), dim3(128), (size_t)(0), st, x, x_stride, w, state, state_stride, qsl, state_slots, N, B, C, \
                                                         taps, act, out, out_stride, rows)
   if (taps == 2) KVF_CONV_CASE(2);
   else if (taps == 3) KVF_CONV_CASE(3);
@@ -143,6 +145,8 @@ template <typename T>
 __global__ void __launch_bounds__(256) conv_state_kernel(const T* __restrict__ x, int x_stride, float* __restrict__ state,
                                                          long long state_stride, const int* __restrict__ qsl,
                                                          const int* __restrict__ state_slots, int C, int taps) {
+  pdl_launch();
+  pdl_wait();
   const int b = blockIdx.x;
   const int first = qsl[b], q_len = qsl[b + 1] - first;
   const int slot = state_slots[b];
@@ -215,6 +219,8 @@ template <> __device__ __forceinline__ float decay_of<bf16>(float rate, float x)
 // CTA lives for microseconds and what counts is how many of them fit an SM
 template <typename T, int R, int KS, bool CH, int PW>
 __global__ void __launch_bounds__(PW == 1 ? 288 : 384, PW == 1 ? 3 : 1) gated_delta_kernel(const DeltaParams p) {
+  pdl_launch();
+  pdl_wait();
   extern __shared__ __align__(16) float sm[];
   constexpr int RP = R + 4;      // a thread's rows in shared memory, padded so that the KS lanes of a column hit other banks
   constexpr int DKS = KS * RP;   // floats of one k, q or g vector in shared memory
@@ -451,7 +457,7 @@ int launch_delta(DeltaParams p, int B, cudaStream_t st) {
     if (e != cudaSuccess) return (int)e;
   }
   dim3 grid(B, p.H, (p.dv + cols - 1) / cols);
-  kern<<<grid, ct + PW * 32, smem, st>>>(p);
+  launch(kern, dim3(grid), dim3(ct + PW * 32), (size_t)(smem), st, p);
   return KVF_LAUNCH_STATUS();
 }
 
@@ -494,6 +500,8 @@ template <typename T>
 __global__ void __launch_bounds__(128) gated_head_norm_kernel(const float* __restrict__ o, int o_stride, const T* __restrict__ gate,
                                                               int gate_stride, const float* __restrict__ w, float eps, int act,
                                                               long long pairs, int H, int dv, T* __restrict__ out, int out_stride) {
+  pdl_launch();
+  pdl_wait();
   const long long pair = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
   if (pair >= pairs) return;
   const int lane = threadIdx.x & 31;
@@ -532,7 +540,7 @@ __global__ void __launch_bounds__(128) gated_head_norm_kernel(const float* __res
     int gy = (C + 255) / 256;                                                                                          \
     if (gy > 65535) gy = 65535;                                                                                        \
     if (rc || taps == 1) return rc;                                                                                    \
-    conv_state_kernel<T><<<dim3(B, gy), 256, 0, st>>>((const T*)x, x_stride, state, state_stride, qsl, state_slots,    \
+    launch(conv_state_kernel<T>, dim3(dim3(B, gy)), dim3(256), (size_t)(0), st, (const T*)x, x_stride, state, state_stride, qsl, state_slots,    \
                                                       C, taps);                                                        \
     return KVF_LAUNCH_STATUS();                                                                                        \
   }                                                                                                                    \
@@ -557,7 +565,7 @@ __global__ void __launch_bounds__(128) gated_head_norm_kernel(const float* __res
     const long long pairs = N * H;                                                                                     \
     if (pairs <= 0) return 0;                                                                                          \
     if (act && !gate) return (int)cudaErrorInvalidValue;                                                               \
-    gated_head_norm_kernel<T><<<dim3((unsigned)((pairs + 3) / 4)), 128, 0, st>>>(o, o_stride, (const T*)gate,           \
+    launch(gated_head_norm_kernel<T>, dim3(dim3((unsigned)((pairs + 3) / 4))), dim3(128), (size_t)(0), st, o, o_stride, (const T*)gate,           \
                                                                                  gate_stride, w, eps, act, pairs, H,   \
                                                                                  dv, (T*)out, out_stride);             \
     return KVF_LAUNCH_STATUS();                                                                                        \

@@ -35,6 +35,8 @@ struct HcParams {
 // S > 0: the number of streams is known at compile time and the streams of a column live in registers
 template <typename T, int SC>
 __global__ void __launch_bounds__(256) hc_step_kernel(const HcParams p, int S_rt) {
+  pdl_launch();
+  pdl_wait();
   extern __shared__ __align__(16) float urow[];  // [W] the read-out u
   __shared__ float red[32];
   __shared__ float s_mix[MAX_STREAMS * MAX_STREAMS], s_out[MAX_STREAMS], s_in[MAX_STREAMS];
@@ -94,6 +96,8 @@ __global__ void __launch_bounds__(256) hc_step_kernel(const HcParams p, int S_rt
 // registers between the sum of squares and the write.  For widths up to 1024 * CPT.
 template <typename T, int SC, int CPT>
 __global__ void __launch_bounds__(1024) hc_step_rows_kernel(const HcParams p) {
+  pdl_launch();
+  pdl_wait();
   __shared__ float red[32];
   __shared__ float s_mix[SC * SC], s_out[SC], s_in[SC];
   const int r = blockIdx.x;
@@ -161,6 +165,8 @@ __global__ void __launch_bounds__(1024) hc_step_rows_kernel(const HcParams p) {
 
 // every stream starts as the embedding's output
 __global__ void replicate_kernel(const float* __restrict__ src, float* __restrict__ streams, int S, int W, size_t total) {
+  pdl_launch();
+  pdl_wait();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const size_t n = i / ((size_t)S * W);
@@ -186,6 +192,8 @@ struct BranchParams {
 // A thread owns at most CPT columns of a row and keeps them in registers for every branch; all loads first.
 template <typename T, int CPT>
 __global__ void __launch_bounds__(1024) branch_norm_mean_rows_kernel(const BranchParams p) {
+  pdl_launch();
+  pdl_wait();
   __shared__ float red[32];
   const size_t n = blockIdx.x;
   const int W = p.W;
@@ -231,6 +239,8 @@ __global__ void __launch_bounds__(1024) branch_norm_mean_rows_kernel(const Branc
 
 template <typename T>
 __global__ void __launch_bounds__(256) branch_norm_mean_kernel(const BranchParams p) {
+  pdl_launch();
+  pdl_wait();
   extern __shared__ __align__(16) float rowbuf[];  // [nb][W]
   __shared__ float red[32];
   const size_t n = blockIdx.x;
@@ -262,6 +272,8 @@ __global__ void __launch_bounds__(256) branch_norm_mean_kernel(const BranchParam
 
 // ---------------------------------------------------------------- soft cap
 __global__ void softcap_kernel(float* __restrict__ x, size_t n, float cap) {
+  pdl_launch();
+  pdl_wait();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) x[i] = cap * tanhf(x[i] / cap);
 }
@@ -277,6 +289,8 @@ __global__ void __launch_bounds__(256) rope_cache_general_kernel(T* __restrict__
                                                                  T* __restrict__ kcache, T* __restrict__ vcache, int nh, int nkv, int dk,
                                                                  int dv, int rot, int interleaved, int block_size,
                                                                  long long num_slots, int* __restrict__ err) {
+  pdl_launch();
+  pdl_wait();
   const int n = blockIdx.x;
   T* row = qkv + (size_t)n * stride;
   const float pos = (float)positions[n];
@@ -329,14 +343,14 @@ int launch_hc(const HcParams& p, int n_rows, int S, cudaStream_t st) {
   if constexpr (SC > 0) {
    if (p.W <= 8192) {
     const dim3 g(n_rows);
-    if (p.W <= 1024) hc_step_rows_kernel<T, SC, 1><<<g, row_threads(p.W, 1), 0, st>>>(p);
-    else if (p.W <= 2048) hc_step_rows_kernel<T, SC, 2><<<g, row_threads(p.W, 2), 0, st>>>(p);
-    else if (p.W <= 4096) hc_step_rows_kernel<T, SC, 4><<<g, row_threads(p.W, 4), 0, st>>>(p);
-    else hc_step_rows_kernel<T, SC, 8><<<g, row_threads(p.W, 8), 0, st>>>(p);
+    if (p.W <= 1024) launch(hc_step_rows_kernel<T, SC, 1>, dim3(g), dim3(row_threads(p.W, 1)), (size_t)(0), st, p);
+    else if (p.W <= 2048) launch(hc_step_rows_kernel<T, SC, 2>, dim3(g), dim3(row_threads(p.W, 2)), (size_t)(0), st, p);
+    else if (p.W <= 4096) launch(hc_step_rows_kernel<T, SC, 4>, dim3(g), dim3(row_threads(p.W, 4)), (size_t)(0), st, p);
+    else launch(hc_step_rows_kernel<T, SC, 8>, dim3(g), dim3(row_threads(p.W, 8)), (size_t)(0), st, p);
     return KVF_LAUNCH_STATUS();
    }
   }
-  hc_step_kernel<T, SC><<<dim3(n_rows), 256, (size_t)p.W * sizeof(float), st>>>(p, S);
+  launch(hc_step_kernel<T, SC>, dim3(dim3(n_rows)), dim3(256), (size_t)((size_t)p.W * sizeof(float)), st, p, S);
   return KVF_LAUNCH_STATUS();
 }
 
@@ -376,10 +390,10 @@ int launch_hc(const HcParams& p, int n_rows, int S, cudaStream_t st) {
     p.nb = nb; p.W = W; p.eps = eps; p.out = out;                                                                      \
     if (W <= 8192) {                                                                                                   \
       const dim3 g((unsigned)N);                                                                                       \
-      if (W <= 1024) branch_norm_mean_rows_kernel<T, 1><<<g, row_threads(W, 1), 0, st>>>(p);                           \
-      else if (W <= 2048) branch_norm_mean_rows_kernel<T, 2><<<g, row_threads(W, 2), 0, st>>>(p);                      \
-      else if (W <= 4096) branch_norm_mean_rows_kernel<T, 4><<<g, row_threads(W, 4), 0, st>>>(p);                      \
-      else branch_norm_mean_rows_kernel<T, 8><<<g, row_threads(W, 8), 0, st>>>(p);                                     \
+      if (W <= 1024) launch(branch_norm_mean_rows_kernel<T, 1>, dim3(g), dim3(row_threads(W, 1)), (size_t)(0), st, p);                           \
+      else if (W <= 2048) launch(branch_norm_mean_rows_kernel<T, 2>, dim3(g), dim3(row_threads(W, 2)), (size_t)(0), st, p);                      \
+      else if (W <= 4096) launch(branch_norm_mean_rows_kernel<T, 4>, dim3(g), dim3(row_threads(W, 4)), (size_t)(0), st, p);                      \
+      else launch(branch_norm_mean_rows_kernel<T, 8>, dim3(g), dim3(row_threads(W, 8)), (size_t)(0), st, p);                                     \
       return KVF_LAUNCH_STATUS();                                                                                      \
     }                                                                                                                  \
     const size_t smem = (size_t)nb * W * sizeof(float);                                                                \
@@ -388,7 +402,7 @@ int launch_hc(const HcParams& p, int n_rows, int S, cudaStream_t st) {
                                            (int)smem);                                                                 \
       if (e != cudaSuccess) return (int)e;                                                                             \
     }                                                                                                                  \
-    branch_norm_mean_kernel<T><<<dim3((unsigned)N), 256, smem, st>>>(p);                                               \
+    launch(branch_norm_mean_kernel<T>, dim3(dim3((unsigned)N)), dim3(256), (size_t)(smem), st, p);                                               \
     return KVF_LAUNCH_STATUS();                                                                                        \
   }                                                                                                                    \
   KVF_API int kvf_rope_cache_general_##SUF(void* qkv, int stride, const int* positions, const float* inv_freq,         \
@@ -397,7 +411,7 @@ int launch_hc(const HcParams& p, int n_rows, int S, cudaStream_t st) {
                                            long long num_slots, int* err, cudaStream_t st) {                           \
     if (N <= 0) return 0;                                                                                              \
     if (rot < 0 || rot > dk || (rot & 1)) return (int)cudaErrorInvalidValue;                                           \
-    rope_cache_general_kernel<T><<<dim3(N), 256, 0, st>>>((T*)qkv, stride, positions, inv_freq, slots, (T*)kcache,     \
+    launch(rope_cache_general_kernel<T>, dim3(dim3(N)), dim3(256), (size_t)(0), st, (T*)qkv, stride, positions, inv_freq, slots, (T*)kcache,     \
                                                           (T*)vcache, nh, nkv, dk, dv, rot, interleaved, block_size,   \
                                                           num_slots, err);                                             \
     return KVF_LAUNCH_STATUS();                                                                                        \
@@ -409,13 +423,20 @@ KVF_STREAMS_API(bf16, bf16)
 KVF_API int kvf_replicate_streams(const float* src, float* streams, long long N, int S, int W, cudaStream_t st) {
   const size_t total = (size_t)N * S * W;
   if (total == 0) return 0;
-  replicate_kernel<<<dim3((unsigned)((total + 255) / 256)), 256, 0, st>>>(src, streams, S, W, total);
+  launch(replicate_kernel, dim3(dim3((unsigned)((total + 255) / 256))), dim3(256), (size_t)(0), st, src, streams, S, W, total);
   return KVF_LAUNCH_STATUS();
 }
 
 KVF_API int kvf_softcap_f32(float* x, long long n, float cap, cudaStream_t st) {
   if (n <= 0) return 0;
   if (!(cap > 0.f)) return (int)cudaErrorInvalidValue;
-  softcap_kernel<<<dim3((unsigned)((n + 255) / 256)), 256, 0, st>>>(x, (size_t)n, cap);
+  launch(softcap_kernel, dim3(dim3((unsigned)((n + 255) / 256))), dim3(256), (size_t)(0), st, x, (size_t)n, cap);
   return KVF_LAUNCH_STATUS();
+}
+
+// Turn programmatic dependent launch on or off for every launch of this library (its own flag: the flag is one
+// per shared library).
+KVF_API int kvf_mixers_set_pdl(int enabled) {
+  kvf::g_pdl_enabled = enabled ? 1 : 0;
+  return 0;
 }

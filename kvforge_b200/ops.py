@@ -44,6 +44,7 @@ _SIGNATURES = {
     "kvf_rope_cache_general_{s}": "pipppppiiiiiiiilpp",
     "kvf_replicate_streams": "ppliip",
     "kvf_softcap_f32": "plfp",
+    "kvf_mixers_set_pdl": "i",
 }
 _CTYPES = {"p": ctypes.c_void_p, "i": ctypes.c_int, "l": ctypes.c_longlong, "f": ctypes.c_float}
 
@@ -70,6 +71,8 @@ def _fn(name: str, lib: str = "core", signature: str | None = None):
         f.argtypes = [_CTYPES[c] for c in sig]
         f.restype = ctypes.c_int
         _bound[key] = f
+        if lib == "mixers" and name != "kvf_mixers_set_pdl":
+            _sync_mixers_pdl()
     return f
 
 
@@ -117,6 +120,18 @@ def set_pdl(enabled: bool) -> None:
     if _pdl_state is not enabled:
         _fn("kvf_set_pdl")(1 if enabled else 0)
         _pdl_state = enabled
+    _sync_mixers_pdl()
+
+
+_mixers_pdl = None
+
+
+def _sync_mixers_pdl() -> None:
+    """The library of the stateful mixers has a flag of its own; it follows the core's once it is loaded."""
+    global _mixers_pdl
+    if "mixers" in native._loaded and _pdl_state is not None and _mixers_pdl is not _pdl_state:
+        _fn("kvf_mixers_set_pdl", "mixers")(1 if _pdl_state else 0)
+        _mixers_pdl = _pdl_state
 
 
 # Kernels of this library launched so far (library matrix products are not counted).
