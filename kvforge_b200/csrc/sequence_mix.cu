@@ -63,6 +63,8 @@ template <typename T> struct VecIO<T, 1> {
 // A thread owns VEC neighbouring channels (one 16-byte load) of `rows` consecutive token rows; TAPS > 0: the
 // taps are known at compile time and a thread keeps its weights in registers.  Each output is one chain of
 // fused multiply-adds over the taps, oldest first, whichever form runs.
+constexpr int CONV_ROWS = 4;  // rows of a tile when a step has many
+
 template <typename T, int VEC, int TAPS>
 __global__ void __launch_bounds__(128) causal_conv_kernel(const T* __restrict__ x, int x_stride, const float* __restrict__ w,
                                                           const float* __restrict__ state, long long state_stride,
@@ -80,6 +82,44 @@ __global__ void __launch_bounds__(128) causal_conv_kernel(const T* __restrict__ 
     for (int e = 0; e < VEC; ++e)
 #pragma unroll
       for (int j = 0; j < TAPS; ++j) wr[e][j] = w[(size_t)(c + e) * TAPS + j];
+  }
+  if (TAPS > 0 && rows == CONV_ROWS) {
+    // all of the tile's rows in one sequence: its rows + taps - 1 inputs are loaded once, together, and every row's
+    // sum slides over them
+    const int n0 = blockIdx.x * CONV_ROWS;
+    const int b0 = n0 < N ? seq_of_row(qsl, B, n0) : -1;
+    if (b0 < 0) return;
+    const int first = qsl[b0], end = qsl[b0 + 1];
+    if (n0 + CONV_ROWS <= end && n0 + CONV_ROWS <= N) {
+      const int slot = state_slots[b0];
+      const float* st = slot >= 0 ? state + (size_t)slot * state_stride : nullptr;
+      const int t0 = n0 - first;
+      constexpr int NIN = CONV_ROWS + (TAPS > 0 ? TAPS : 1) - 1;
+      float u[NIN][VEC];
+#pragma unroll
+      for (int i = 0; i < NIN; ++i) {
+        const int src = t0 - (TAPS - 1) + i;
+        if (src >= 0) {
+          VecIO<T, VEC>::load(x + (size_t)(first + src) * x_stride + c, u[i]);
+        } else {
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) u[i][e] = st ? st[(size_t)(TAPS - 1 + src) * C + c + e] : 0.f;
+        }
+      }
+#pragma unroll
+      for (int rr = 0; rr < CONV_ROWS; ++rr) {
+        float acc[VEC];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          acc[e] = 0.f;
+#pragma unroll
+          for (int j = 0; j < (TAPS > 0 ? TAPS : 1); ++j) acc[e] = fmaf(wr[e][j], u[rr + j][e], acc[e]);
+          if (act == 1) acc[e] = silu_f(acc[e]);
+        }
+        VecIO<T, VEC>::store(out + (size_t)(n0 + rr) * out_stride + c, acc);
+      }
+      return;
+    }
   }
   for (int rr = 0; rr < rows; ++rr) {
     const int n = blockIdx.x * rows + rr;
@@ -118,7 +158,7 @@ __global__ void __launch_bounds__(128) causal_conv_kernel(const T* __restrict__ 
 template <typename T, int VEC>
 int launch_conv(const T* x, int x_stride, const float* w, const float* state, long long state_stride, const int* qsl,
                 const int* state_slots, int N, int B, int C, int taps, int act, T* out, int out_stride, cudaStream_t st) {
-  const int rows = N >= 1024 ? 4 : 1;
+  const int rows = N >= 1024 ? CONV_ROWS : 1;
   const int per_cta = 128 * VEC;
   dim3 grid((N + rows - 1) / rows, (C + per_cta - 1) / per_cta);
   if (grid.y > 65535u) return (int)cudaErrorInvalidValue;
@@ -345,9 +385,20 @@ __global__ void __launch_bounds__(PW == 1 ? 288 : 384, PW == 1 ? 3 : 1) gated_de
   } else {
     // the state's tile [dk][cols] through shared memory (it borrows the second buffer, which is filled only later)
     float* stage = buf1;
-    for (int idx = threadIdx.x; idx < dk * cols; idx += CT) {
-      const int r = idx / cols, c = idx - r * cols;
-      stage[r * (cols + 1) + c] = (col0 + c < dv) ? sg[(size_t)r * dv + col0 + c] : 0.f;
+    for (int base = 0; base < dk * cols; base += 8 * CT) {  // eight loads of a thread in flight at once
+      float tmp[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int idx = base + i * CT + threadIdx.x;
+        const int r = idx / cols, c = idx - r * cols;
+        tmp[i] = (idx < dk * cols && col0 + c < dv) ? sg[(size_t)r * dv + col0 + c] : 0.f;
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int idx = base + i * CT + threadIdx.x;
+        const int r = idx / cols, c = idx - r * cols;
+        if (idx < dk * cols) stage[r * (cols + 1) + c] = tmp[i];
+      }
     }
     asm volatile("bar.sync 1, %0;" ::"r"(CT) : "memory");
 #pragma unroll

@@ -191,7 +191,7 @@ struct BranchParams {
 
 // A thread owns at most CPT columns of a row and keeps them in registers for every branch; all loads first.
 template <typename T, int CPT>
-__global__ void __launch_bounds__(1024) branch_norm_mean_rows_kernel(const BranchParams p) {
+__global__ void __launch_bounds__(256) branch_norm_mean_rows_kernel(const BranchParams p) {
   pdl_launch();
   pdl_wait();
   __shared__ float red[32];
@@ -211,6 +211,14 @@ __global__ void __launch_bounds__(1024) branch_norm_mean_rows_kernel(const Branc
       }
     }
   }
+  float wv[MAX_BRANCHES][CPT];
+#pragma unroll
+  for (int b = 0; b < MAX_BRANCHES; ++b)
+#pragma unroll
+    for (int k = 0; k < CPT; ++k) {
+      const int c = threadIdx.x + k * blockDim.x;
+      wv[b][k] = (b < p.nb && c < W) ? p.w[b][c] : 0.f;
+    }
   float inv[MAX_BRANCHES];
 #pragma unroll
   for (int b = 0; b < MAX_BRANCHES; ++b) {
@@ -232,7 +240,7 @@ __global__ void __launch_bounds__(1024) branch_norm_mean_rows_kernel(const Branc
     float acc = 0.f;
 #pragma unroll
     for (int b = 0; b < MAX_BRANCHES; ++b)
-      if (b < p.nb) acc += v[b][k] * inv[b] * p.w[b][c];
+      if (b < p.nb) acc += v[b][k] * inv[b] * wv[b][k];
     o[c] = from_float<T>(acc * share);
   }
 }
@@ -390,10 +398,12 @@ int launch_hc(const HcParams& p, int n_rows, int S, cudaStream_t st) {
     p.nb = nb; p.W = W; p.eps = eps; p.out = out;                                                                      \
     if (W <= 8192) {                                                                                                   \
       const dim3 g((unsigned)N);                                                                                       \
-      if (W <= 1024) launch(branch_norm_mean_rows_kernel<T, 1>, dim3(g), dim3(row_threads(W, 1)), (size_t)(0), st, p);                           \
-      else if (W <= 2048) launch(branch_norm_mean_rows_kernel<T, 2>, dim3(g), dim3(row_threads(W, 2)), (size_t)(0), st, p);                      \
-      else if (W <= 4096) launch(branch_norm_mean_rows_kernel<T, 4>, dim3(g), dim3(row_threads(W, 4)), (size_t)(0), st, p);                      \
-      else launch(branch_norm_mean_rows_kernel<T, 8>, dim3(g), dim3(row_threads(W, 8)), (size_t)(0), st, p);                                     \
+      /* small CTAs, so that many rows share an SM and their loads overlap */                                          \
+      if (W <= 256) launch(branch_norm_mean_rows_kernel<T, 1>, g, dim3(row_threads(W, 1)), 0, st, p);                  \
+      else if (W <= 1024) launch(branch_norm_mean_rows_kernel<T, 4>, g, dim3(row_threads(W, 4)), 0, st, p);            \
+      else if (W <= 2048) launch(branch_norm_mean_rows_kernel<T, 8>, g, dim3(row_threads(W, 8)), 0, st, p);            \
+      else if (W <= 4096) launch(branch_norm_mean_rows_kernel<T, 16>, g, dim3(row_threads(W, 16)), 0, st, p);          \
+      else launch(branch_norm_mean_rows_kernel<T, 32>, g, dim3(row_threads(W, 32)), 0, st, p);                         \
       return KVF_LAUNCH_STATUS();                                                                                      \
     }                                                                                                                  \
     const size_t smem = (size_t)nb * W * sizeof(float);                                                                \

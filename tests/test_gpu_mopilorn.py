@@ -299,6 +299,38 @@ def test_short_convolution_with_state(dtype, taps, act):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("taps", [2, 4, 5])
+def test_short_convolution_of_a_step_with_many_rows(dtype, taps):
+    """More than a thousand rows in a step: rows come in tiles of four; a tile inside one sequence loads its inputs
+    once, a tile that crosses from one sequence into the next (or ends the step) takes the rows one by one.  Both
+    must give the same sums; the second step continues from the state the first left."""
+    from kvforge_b200 import ops
+
+    dev, dt = "cuda", DT[dtype]
+    c = 72
+    g = torch.Generator().manual_seed(taps)
+    w = torch.randn(c, taps, generator=g)
+    lens = [(701, 38), (9, 5), (602, 0), (3, 30)]
+    seqs = [torch.randn(a + b, c, generator=g).to(dt).float() for a, b in lens]
+    want = [plain.short_conv(u.double(), w.double()) for u in seqs]
+    state = torch.zeros(5, (taps - 1) * c, device=dev)
+    got = [[] for _ in seqs]
+    for step in range(2):
+        ls = [ab[step] for ab in lens]
+        x = torch.cat([u[: ls[i]] if step == 0 else u[lens[i][0] :] for i, u in enumerate(seqs)]).to(dev, dt)
+        qsl, sl = flat_batch(ls, [3, 0, 4, 1], dev)
+        out = torch.empty_like(x)
+        ops.causal_conv(x, w.to(dev), state, qsl, sl, 4, out)
+        o = 0
+        for i in range(4):
+            got[i].append(out[o : o + ls[i]].float().cpu())
+            o += ls[i]
+    tol = 1e-5 if dtype == "float32" else 2e-2
+    for i in range(4):
+        assert torch.allclose(torch.cat(got[i]).double(), want[i], atol=tol, rtol=tol)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("h,g,dk,dv,channel", [(4, 2, 16, 8, False), (3, 3, 24, 40, True), (2, 1, 64, 32, True), (2, 2, 128, 128, False), (1, 1, 8, 300, True)])
 def test_gated_delta_rule_through_the_state(dtype, h, g, dk, dv, channel):
     """Two sequences cut into steps (single tokens among them) against the rule applied token by token to
