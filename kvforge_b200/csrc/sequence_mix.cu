@@ -217,10 +217,12 @@ __global__ void __launch_bounds__(256) conv_state_kernel(const T* __restrict__ x
 // with the decayed state, (S^T k) and (S^T q), in split accumulators; two shuffle trees run side by
 // side; then u = beta (v - S^T k), the read-out is o = S^T q + u (k . q) (the same as reading after
 // the write, with k . q taken once per token), and the write is one fused multiply-add per row with
-// the keys still in registers.  Tokens come in chunks through two buffers of shared memory: four
-// producer warps load a chunk's k, q, v and logits with all their loads in flight at once, norm
-// them, and compute beta, g and k . q, while the consumer warps walk the chunk before.  The state
-// goes through shared memory on its way in and out, so that global memory sees whole rows of a tile.
+// the keys still in registers.  What does not depend on the state (unit k and q, beta, g, k . q) is
+// made before the walk by a kernel of its own, a warp per (token, head), so that no CTA of the walk
+// repeats it for its tile of columns.  Tokens come in chunks through two buffers of shared memory:
+// producer warps copy a chunk's vectors there (cp.async) while the consumer warps walk the chunk
+// before.  The state goes through shared memory on its way in and out, so that global memory sees
+// whole rows of a tile.
 struct DeltaParams {
   const void* q;  // [N][G*dk] after convolution and activation
   const void* k;
@@ -243,6 +245,14 @@ struct DeltaParams {
   float q_scale, norm_eps;
   int chunk;       // tokens per chunk (a multiple of the producer warps)
   int buf_floats;  // floats of one chunk buffer
+  // what the walk reads of a token besides v, made by the prepare kernel: unit keys and unit, scaled queries
+  // [N][H][dk], the decay per key channel [N][H][dk] (per-channel form), and per (token, head) beta, k.q and
+  // the head's decay [N][H][4]
+  float* kn;
+  float* qn;
+  float* gn;
+  float* sc;
+  int N;
 };
 
 // exp(rate * softplus(x)), rate < 0: exact library functions in 32-bit storage; in bfloat16 storage the fast
@@ -255,6 +265,57 @@ template <> __device__ __forceinline__ float decay_of<bf16>(float rate, float x)
   return __expf(rate * (x > 20.f ? x : __logf(1.f + __expf(x))));
 }
 
+// Everything of a token that does not depend on the state, computed once, a warp per (token, head), by as many
+// warps as the step has such pairs: the walk itself then only copies.
+template <typename T>
+__global__ void __launch_bounds__(128) delta_prepare_kernel(const DeltaParams p) {
+  pdl_launch();
+  pdl_wait();
+  const long long pair = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (pair >= (long long)p.N * p.H) return;
+  const int lane = threadIdx.x & 31;
+  const size_t n = (size_t)(pair / p.H);
+  const int h = (int)(pair - (long long)n * p.H);
+  const int dk = p.dk, kvh = h / (p.H / p.G);
+  const T* kr = (const T*)p.k + n * p.qkv_stride + (size_t)kvh * dk;
+  const T* qr = (const T*)p.q + n * p.qkv_stride + (size_t)kvh * dk;
+  float sk = 0.f, sq = 0.f, kq = 0.f;
+#pragma unroll 4
+  for (int r = lane; r < dk; r += 32) {
+    const float kv = to_float<T>(kr[r]), qv = to_float<T>(qr[r]);
+    sk = fmaf(kv, kv, sk);
+    sq = fmaf(qv, qv, sq);
+    kq = fmaf(kv, qv, kq);
+  }
+  sk = warp_sum(sk);
+  sq = warp_sum(sq);
+  kq = warp_sum(kq);
+  const float ik = 1.f / sqrtf(sk + p.norm_eps), iq = p.q_scale / sqrtf(sq + p.norm_eps);
+  const float neg_rate = -expf(p.A_log[h]);
+  float* ko = p.kn + ((size_t)n * p.H + h) * dk;
+  float* qo = p.qn + ((size_t)n * p.H + h) * dk;
+  float* go = p.gn ? p.gn + ((size_t)n * p.H + h) * dk : nullptr;
+  const float* ar = p.a + n * p.a_stride + (size_t)h * dk;
+#pragma unroll 4
+  for (int r = lane; r < dk; r += 32) {
+    ko[r] = to_float<T>(kr[r]) * ik;
+    qo[r] = to_float<T>(qr[r]) * iq;
+    if (p.per_channel) go[r] = decay_of<T>(neg_rate, ar[r] + p.dt_bias[(size_t)h * dk + r]);
+  }
+  if (lane == 0) {
+    float* so = p.sc + ((size_t)n * p.H + h) * 4;
+    so[0] = sigmoid_f(p.b[n * p.b_stride + h]);
+    so[1] = kq * ik * iq;
+    so[2] = p.per_channel ? 1.f : decay_of<T>(neg_rate, p.a[n * p.a_stride + h] + p.dt_bias[h]);
+    so[3] = 0.f;
+  }
+}
+
+__device__ __forceinline__ void cp_async16(float* smem_dst, const float* gsrc) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gsrc) : "memory");
+}
+
 // PW producer warps: 4 for walks over many tokens; 1 for steps of a few tokens a sequence (decoding), where a
 // CTA lives for microseconds and what counts is how many of them fit an SM
 template <typename T, int R, int KS, bool CH, int PW>
@@ -265,8 +326,6 @@ __global__ void __launch_bounds__(PW == 1 ? 288 : 384, PW == 1 ? 3 : 1) gated_de
   constexpr int RP = R + 4;      // a thread's rows in shared memory, padded so that the KS lanes of a column hit other banks
   constexpr int DKS = KS * RP;   // floats of one k, q or g vector in shared memory
   constexpr int DKP = R * KS;    // rows a column's threads cover; rows >= dk hold k = q = 0
-  constexpr int DPL = (DKP + 31) / 32;  // elements of a vector per producer lane
-  constexpr int JB = DPL <= 4 ? 4 : (DPL <= 8 ? 2 : 1);  // tokens a producer warp loads at once
   const int b = blockIdx.x, h = blockIdx.y;
   const int first = p.qsl[b], q_len = p.qsl[b + 1] - first;
   const int slot = p.state_slots[b];
@@ -274,7 +333,6 @@ __global__ void __launch_bounds__(PW == 1 ? 288 : 384, PW == 1 ? 3 : 1) gated_de
   const int CT = blockDim.x - PW * 32;  // consumer threads
   const int cols = CT / KS;
   const int dk = p.dk, dv = p.dv, TB = p.chunk;
-  const int kvh = h / (p.H / p.G);
   const bool producer = threadIdx.x >= CT;
   // layout of a chunk buffer: k [TB][DKS], q [TB][DKS], (g [TB][DKS],) v [TB][cols], beta [TB], k.q [TB], g of the head [TB]
   const int off_q = TB * DKS, off_g = 2 * TB * DKS, off_v = (CH ? 3 : 2) * TB * DKS;
@@ -283,95 +341,52 @@ __global__ void __launch_bounds__(PW == 1 ? 288 : 384, PW == 1 ? 3 : 1) gated_de
   const int col0 = blockIdx.z * cols;
   const int nchunks = (q_len + TB - 1) / TB;
 
-  // ---- producers: chunk c into buffer `buf`.  Every global load of a warp's tokens is issued before the first
-  // of them is used (a load that is waited for alone costs most of a microsecond, and there would be a dozen per
-  // chunk); what does not change from token to token is loaded once.
-  const int pt = threadIdx.x - CT, pwarp = pt >> 5, plane = pt & 31;
-  float bias[DPL];
-  float neg_rate = 0.f, bias_h = 0.f;
-  if (producer) {
-    neg_rate = -expf(p.A_log[h]);
-    if (!CH) bias_h = p.dt_bias[h];
-#pragma unroll
-    for (int e = 0; e < DPL; ++e) {
-      const int r = plane + 32 * e;
-      bias[e] = (CH && r < dk) ? p.dt_bias[(size_t)h * dk + r] : 0.f;
-    }
-  }
+  // ---- producers: chunk c into buffer `buf`: copies of what the prepare kernel made (16 bytes a copy, straight
+  // into shared memory, four rows of a vector at a time, which the padded layout keeps together) and this CTA's
+  // columns of v.  Rows from dk up to DKP of k and q stay zero and of g one: they are set once, below.
+  const int pt = threadIdx.x - CT;
   auto prepare = [&](int c, float* buf) {
-    const int warp = pwarp, lane = plane;
     const int t0 = c * TB, nt = min(TB, q_len - t0);
-    const T* qg = (const T*)p.q;
-    const T* kg = (const T*)p.k;
     const T* vg = (const T*)p.v;
-    for (int j0 = 0; j0 * PW < TB; j0 += JB) {
-      float kv[JB][DPL], qv[JB][DPL], av[JB][DPL], bl[JB], al[JB];
-#pragma unroll
-      for (int j = 0; j < JB; ++j) {
-        const int tt = warp + (j0 + j) * PW;
-        const size_t n = (size_t)(first + t0 + (tt < nt ? tt : 0));
-        const T* kr = kg + n * p.qkv_stride + (size_t)kvh * dk;
-        const T* qr = qg + n * p.qkv_stride + (size_t)kvh * dk;
-        const float* ar = p.a + n * p.a_stride + (size_t)h * dk;
-#pragma unroll
-        for (int e = 0; e < DPL; ++e) {
-          const int r = lane + 32 * e;
-          const bool ok = r < dk && tt < nt;
-          kv[j][e] = ok ? to_float<T>(kr[r]) : 0.f;
-          qv[j][e] = ok ? to_float<T>(qr[r]) : 0.f;
-          if (CH) av[j][e] = ok ? ar[r] : 0.f;
-        }
-        bl[j] = p.b[n * p.b_stride + h];
-        al[j] = CH ? 0.f : p.a[n * p.a_stride + h];
+    const int nvec = CH ? 3 : 2;
+    if ((dk & 3) == 0) {
+      const int q4 = dk >> 2;  // copies per vector
+      for (int idx = pt; idx < nt * nvec * q4; idx += PW * 32) {
+        const int tt = idx / (nvec * q4), rem = idx - tt * (nvec * q4);
+        const int which = rem / q4, r = (rem - which * q4) << 2;
+        const float* src = (which == 0 ? p.kn : which == 1 ? p.qn : p.gn) + ((size_t)(first + t0 + tt) * p.H + h) * dk + r;
+        cp_async16(buf + which * TB * DKS + tt * DKS + (r / R) * RP + (r % R), src);
       }
-      // this CTA's columns of v: a thread's elements of the chunk, loaded together
-      constexpr int VPT = 4;
-      for (int base = 0; base < nt * cols && j0 == 0; base += VPT * PW * 32) {
-        float vv[VPT];
-#pragma unroll
-        for (int i = 0; i < VPT; ++i) {
-          const int idx = base + i * PW * 32 + pt;
-          const int tt = idx / cols, cc = col0 + (idx - tt * cols);
-          vv[i] = (idx < nt * cols && cc < dv) ? to_float<T>(vg[(size_t)(first + t0 + tt) * p.qkv_stride + (size_t)h * dv + cc]) : 0.f;
-        }
-#pragma unroll
-        for (int i = 0; i < VPT; ++i) {
-          const int idx = base + i * PW * 32 + pt;
-          if (idx < nt * cols) buf[off_v + idx] = vv[i];
-        }
-      }
-#pragma unroll
-      for (int j = 0; j < JB; ++j) {
-        const int tt = warp + (j0 + j) * PW;
-        if (tt >= nt) continue;  // warp-uniform
-        float sk = 0.f, sq = 0.f, kq = 0.f;
-#pragma unroll
-        for (int e = 0; e < DPL; ++e) {
-          sk = fmaf(kv[j][e], kv[j][e], sk);
-          sq = fmaf(qv[j][e], qv[j][e], sq);
-          kq = fmaf(kv[j][e], qv[j][e], kq);
-        }
-        sk = warp_sum(sk);
-        sq = warp_sum(sq);
-        kq = warp_sum(kq);
-        const float ik = 1.f / sqrtf(sk + p.norm_eps), iq = p.q_scale / sqrtf(sq + p.norm_eps);
-#pragma unroll
-        for (int e = 0; e < DPL; ++e) {
-          const int r = lane + 32 * e;
-          if (r < DKP) {
-            const int at = tt * DKS + (r / R) * RP + (r % R);
-            buf[at] = kv[j][e] * ik;
-            buf[off_q + at] = qv[j][e] * iq;
-            if (CH) buf[off_g + at] = r < dk ? decay_of<T>(neg_rate, av[j][e] + bias[e]) : 1.f;
-          }
-        }
-        if (lane == 0) {
-          buf[off_beta + tt] = sigmoid_f(bl[j]);
-          buf[off_kq + tt] = kq * ik * iq;
-          if (!CH) buf[off_gh + tt] = decay_of<T>(neg_rate, al[j] + bias_h);
-        }
+    } else {
+      for (int idx = pt; idx < nt * nvec * dk; idx += PW * 32) {
+        const int tt = idx / (nvec * dk), rem = idx - tt * (nvec * dk);
+        const int which = rem / dk, r = rem - which * dk;
+        const float* src = (which == 0 ? p.kn : which == 1 ? p.qn : p.gn) + ((size_t)(first + t0 + tt) * p.H + h) * dk + r;
+        buf[which * TB * DKS + tt * DKS + (r / R) * RP + (r % R)] = *src;
       }
     }
+    constexpr int VPT = 4;
+    for (int base = 0; base < nt * cols; base += VPT * PW * 32) {
+      float vv[VPT];
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int idx = base + i * PW * 32 + pt;
+        const int tt = idx / cols, cc = col0 + (idx - tt * cols);
+        vv[i] = (idx < nt * cols && cc < dv) ? to_float<T>(vg[(size_t)(first + t0 + tt) * p.qkv_stride + (size_t)h * dv + cc]) : 0.f;
+      }
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int idx = base + i * PW * 32 + pt;
+        if (idx < nt * cols) buf[off_v + idx] = vv[i];
+      }
+    }
+    if (pt < nt) {
+      const float4 sc4 = *reinterpret_cast<const float4*>(p.sc + ((size_t)(first + t0 + pt) * p.H + h) * 4);
+      buf[off_beta + pt] = sc4.x;
+      buf[off_kq + pt] = sc4.y;
+      buf[off_gh + pt] = sc4.z;
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");
   };
 
   float* buf0 = sm;
@@ -380,11 +395,18 @@ __global__ void __launch_bounds__(PW == 1 ? 288 : 384, PW == 1 ? 3 : 1) gated_de
   const int col = col0 + cl;
   const bool live = !producer && col < dv;
   float S[R];
+  if (dk < DKP) {  // rows that no copy ever writes: keys and queries zero, decay one
+    for (int idx = threadIdx.x; idx < 2 * p.buf_floats; idx += blockDim.x) {
+      const int in_buf = idx % p.buf_floats;
+      sm[idx] = (CH && in_buf >= off_g && in_buf < off_v) ? 1.f : 0.f;
+    }
+    __syncthreads();
+  }
   if (producer) {
     prepare(0, buf0);
   } else {
-    // the state's tile [dk][cols] through shared memory (it borrows the second buffer, which is filled only later)
-    float* stage = buf1;
+    // the state's tile [dk][cols] through shared memory (a region of its own behind the two chunk buffers)
+    float* stage = sm + 2 * p.buf_floats;
     for (int base = 0; base < dk * cols; base += 8 * CT) {  // eight loads of a thread in flight at once
       float tmp[8];
 #pragma unroll
@@ -463,7 +485,7 @@ __global__ void __launch_bounds__(PW == 1 ? 288 : 384, PW == 1 ? 3 : 1) gated_de
     __syncthreads();
   }
   if (!producer) {
-    float* stage = buf0;  // both buffers are free now
+    float* stage = sm + 2 * p.buf_floats;
 #pragma unroll
     for (int i = 0; i < R; ++i) {
       const int r = ks * R + i;
@@ -494,11 +516,10 @@ int launch_delta(DeltaParams p, int B, cudaStream_t st) {
   const int cols = ct / KS;
   const int per_token = (CH ? 3 : 2) * DKS + cols + 3;
   int chunk = PW == 1 ? 4 : 16;
-  while (chunk > PW && (size_t)2 * chunk * per_token * sizeof(float) > 96 * 1024) chunk -= PW;
-  int buf_floats = (chunk * per_token + 3) / 4 * 4;
+  while (chunk > PW && (size_t)2 * chunk * per_token * sizeof(float) > 80 * 1024) chunk -= PW;
+  const int buf_floats = (chunk * per_token + 3) / 4 * 4;
   const int stage = p.dk * (cols + 1);
-  if (buf_floats < stage) buf_floats = (stage + 3) / 4 * 4;
-  const size_t smem = (size_t)2 * buf_floats * sizeof(float);
+  const size_t smem = ((size_t)2 * buf_floats + stage) * sizeof(float);
   if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
   p.chunk = chunk;
   p.buf_floats = buf_floats;
@@ -539,6 +560,10 @@ int dispatch_delta_rows(const DeltaParams& p, int B, cudaStream_t st) {
 
 template <typename T>
 int dispatch_delta(const DeltaParams& p, int B, int max_q_len, cudaStream_t st) {
+  const long long pairs = (long long)p.N * p.H;
+  if (pairs <= 0) return 0;
+  int rc = launch(delta_prepare_kernel<T>, dim3((unsigned)((pairs + 3) / 4)), dim3(128), 0, st, p);
+  if (rc) return rc;
   const bool few = max_q_len > 0 && max_q_len <= 4;
   if (p.per_channel) return few ? dispatch_delta_rows<T, true, 1>(p, B, st) : dispatch_delta_rows<T, true, 4>(p, B, st);
   return few ? dispatch_delta_rows<T, false, 1>(p, B, st) : dispatch_delta_rows<T, false, 4>(p, B, st);
@@ -599,8 +624,8 @@ __global__ void __launch_bounds__(128) gated_head_norm_kernel(const float* __res
                                     int b_stride, const float* a, int a_stride, const float* A_log,                    \
                                     const float* dt_bias, int per_channel, float* state, long long state_stride,       \
                                     float* out, int out_stride, const int* qsl, const int* state_slots, int B, int H,  \
-                                    int G, int dk, int dv, float q_scale, float norm_eps, int max_q_len,               \
-                                    cudaStream_t st) {                                                                 \
+                                    int G, int dk, int dv, float q_scale, float norm_eps, int max_q_len, int N,        \
+                                    float* kn, float* qn, float* gn, float* sc, cudaStream_t st) {                     \
     if (B <= 0) return 0;                                                                                              \
     if (H <= 0 || G <= 0 || H % G || dk <= 0 || dv <= 0 || (unsigned)H > 65535u) return (int)cudaErrorInvalidValue;    \
     DeltaParams p;                                                                                                     \
@@ -608,6 +633,8 @@ __global__ void __launch_bounds__(128) gated_head_norm_kernel(const float* __res
     p.a_stride = a_stride; p.A_log = A_log; p.dt_bias = dt_bias; p.per_channel = per_channel; p.state = state;         \
     p.state_stride = state_stride; p.out = out; p.out_stride = out_stride; p.qsl = qsl; p.state_slots = state_slots;   \
     p.H = H; p.G = G; p.dk = dk; p.dv = dv; p.q_scale = q_scale; p.norm_eps = norm_eps; p.chunk = 1; p.buf_floats = 0;  \
+    p.kn = kn; p.qn = qn; p.gn = gn; p.sc = sc; p.N = N;                                                               \
+    if (!kn || !qn || !sc || (per_channel && !gn)) return (int)cudaErrorInvalidValue;                                  \
     return dispatch_delta<T>(p, B, max_q_len, st);                                                                     \
   }                                                                                                                    \
   KVF_API int kvf_gated_head_norm_##SUF(const float* o, int o_stride, const void* gate, int gate_stride,               \

@@ -37,7 +37,7 @@ _SIGNATURES = {
     "kvf_argmax_f32": "pliipipp",
     # library "mixers"
     "kvf_causal_conv_{s}": "pipplppiiiiipip",
-    "kvf_gated_delta_{s}": "pppipipippiplpippiiiiiffip",
+    "kvf_gated_delta_{s}": "pppipipippiplpippiiiiiffiippppp",
     "kvf_gated_head_norm_{s}": "pipipfiliipip",
     "kvf_hc_step_{s}": "pppilppppppiiifp",
     "kvf_branch_norm_mean_{s}": "pppppilifpp",
@@ -980,7 +980,7 @@ def gated_delta(
     q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta_logits: torch.Tensor, step_logits: torch.Tensor,
     a_log: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor, out: torch.Tensor, qsl: torch.Tensor,
     state_slots: torch.Tensor, num_seqs: int, num_heads: int, num_kv_heads: int, dk: int, dv: int, q_scale: float,
-    norm_eps: float = 1e-6, max_query_len: int = 0,
+    norm_eps: float = 1e-6, max_query_len: int = 0, scratch: tuple[torch.Tensor, ...] | None = None,
 ) -> None:  # fmt: skip
     """The gated delta rule over a flat batch, token by token per sequence, on the state
     ``S [heads, dk, dv]`` of each sequence's slot (``csrc/sequence_mix.cu`` has the equations).
@@ -989,7 +989,10 @@ def gated_delta(
     ``beta_logits`` float ``[N, H]``; ``step_logits`` float ``[N, H]`` (one decay a head) or
     ``[N, H*dk]`` (one a key channel), with ``dt_bias`` of the same width and ``a_log [H]``;
     ``out`` float ``[N, H*dv]`` gets the read-out.  ``max_query_len`` (0 = unknown): the most rows any
-    sequence of the step brings; up to 4 the kernel takes the form made for steps of single tokens."""
+    sequence of the step brings; up to 4 the kernel takes the form made for steps of single tokens.
+    ``scratch``: float buffers ``(kn [N, H*dk], qn [N, H*dk], gn [N, H*dk] or None, sc [N, H*4])`` for what
+    a kernel of its own makes of every token before the walk (unit k and q, decays, beta, k.q); without it
+    they are allocated here (tests; a step of the engine passes persistent buffers).  Two launches."""
     s = _suffix(q.dtype)
     h, g = int(num_heads), int(num_kv_heads)
     for t, w, what in ((q, g * dk, "q"), (k, g * dk, "k"), (v, h * dv, "v")):
@@ -1010,14 +1013,26 @@ def gated_delta(
     sptr, sstride = _state_view(state, h * dk * dv, "delta state")
     _need(qsl, torch.int32, "query_start_loc")
     _need(state_slots, torch.int32, "state_slots")
+    if scratch is None:
+        mk = lambda w: torch.empty((n, w), dtype=torch.float32, device=q.device)  # noqa: E731
+        scratch = (mk(h * dk), mk(h * dk), mk(h * dk) if per_channel else None, mk(h * 4))
+    kn, qn, gn, sc = scratch
+    for t, w, what in ((kn, h * dk, "kn"), (qn, h * dk, "qn"), (gn, h * dk, "gn"), (sc, h * 4, "sc")):
+        if t is None and what == "gn" and not per_channel:
+            continue
+        _need(t, torch.float32, f"scratch {what}")
+        if tuple(t.shape) != (n, w):
+            raise ValueError(f"gated_delta: scratch {what} must be float [{n}, {w}]")
     name = f"kvf_gated_delta_{s}"
     _check(
         _fn(name, MIXERS_LIB)(
             _ptr(q), _ptr(k), _ptr(v), q.stride(0), _ptr(beta_logits), beta_logits.stride(0), _ptr(step_logits),
             step_logits.stride(0), _ptr(a_log), _ptr(dt_bias), 1 if per_channel else 0, sptr, sstride, _ptr(out),
-            out.stride(0), _ptr(qsl), _ptr(state_slots), num_seqs, h, g, dk, dv, float(q_scale), float(norm_eps), int(max_query_len), _stream(),
+            out.stride(0), _ptr(qsl), _ptr(state_slots), num_seqs, h, g, dk, dv, float(q_scale), float(norm_eps), int(max_query_len),
+            n, _ptr(kn), _ptr(qn), _ptr(gn) if per_channel else None, _ptr(sc), _stream(),
         ),
         name,
+        2,
     )  # fmt: skip
 
 

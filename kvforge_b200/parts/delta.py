@@ -165,10 +165,15 @@ class GatedDeltaRule(Mixer):
         else:
             gate = main[:, self.off_gate : self.off_gate + self.c_v]
         read = rt.buf("delta.read", n, self.c_v, torch.float32)
+        f32 = torch.float32
+        scratch = (
+            rt.buf("delta.kn", n, H * dk, f32), rt.buf("delta.qn", n, H * dk, f32),
+            rt.buf("delta.gn", n, H * dk, f32) if self.decay == "channel" else None, rt.buf("delta.sc", n, H * 4, f32),
+        )  # fmt: skip
         ops.gated_delta(
             qkv[:, : self.c_q], qkv[:, self.c_q : 2 * self.c_q], qkv[:, 2 * self.c_q :], small[:, :H], step, self.a_log, self.dt_bias,
             cache.state[:, self.conv_floats :], read, ctx.query_start_loc, ctx.state_slots, ctx.num_seqs, H, self.G, dk, dv,
-            q_scale=dk**-0.5, norm_eps=1e-6, max_query_len=ctx.max_query_len,
+            q_scale=dk**-0.5, norm_eps=1e-6, max_query_len=ctx.max_query_len, scratch=scratch,
         )  # fmt: skip
         y = rt.buf("delta.y", n, self.c_v)
         ops.gated_head_norm(read, gate, self.norm_w, self.eps, y, H, dv, activation=self.gate)
