@@ -121,7 +121,8 @@ __global__ void __launch_bounds__(1024) hc_step_rows_kernel(const HcParams p) {
     nw[k] = c < W ? p.norm_w[c] : 0.f;
   }
   if (pr) {
-    for (int sl = 0; sl < p.nsplit; ++sl) {
+#pragma unroll 4
+    for (int sl = 0; sl < p.nsplit; ++sl) {  // several slices' loads in flight; each column's sum in slice order
 #pragma unroll
       for (int k = 0; k < CPT; ++k) {
         const int c = threadIdx.x + k * blockDim.x;
@@ -203,11 +204,17 @@ __global__ void __launch_bounds__(256) branch_norm_mean_rows_kernel(const Branch
 #pragma unroll
     for (int k = 0; k < CPT; ++k) {
       const int c = threadIdx.x + k * blockDim.x;
-      v[b][k] = 0.f;
-      if (b < p.nb && c < W) {
-        if (p.y[b]) v[b][k] = to_float<T>(((const T*)p.y[b])[n * W + c]);
-        else
-          for (int sl = 0; sl < p.nsplit[b]; ++sl) v[b][k] += p.partials[b][n * W + (size_t)sl * p.split_stride[b] + c];
+      v[b][k] = (b < p.nb && c < W && p.y[b]) ? to_float<T>(((const T*)p.y[b])[n * W + c]) : 0.f;
+    }
+    if (b < p.nb && !p.y[b]) {
+      const float* pr = p.partials[b] + n * W;
+#pragma unroll 4
+      for (int sl = 0; sl < p.nsplit[b]; ++sl) {  // a slice's columns together, several slices in flight
+#pragma unroll
+        for (int k = 0; k < CPT; ++k) {
+          const int c = threadIdx.x + k * blockDim.x;
+          if (c < W) v[b][k] += pr[(size_t)sl * p.split_stride[b] + c];
+        }
       }
     }
   }
