@@ -258,15 +258,14 @@ def flat_batch(lengths, slots, device):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("taps,act", [(4, "silu"), (2, None), (3, None)])
-def test_short_convolution_with_state(dtype, taps, act):
+@pytest.mark.parametrize("taps,act,c", [(4, "silu", 40), (2, None, 40), (3, None, 40), (3, "silu", 30), (6, None, 36)])
+def test_short_convolution_with_state(dtype, taps, act, c):
     """Three sequences cut into steps of unequal lengths (one shorter than the taps, one left out of a step,
     one padding sequence without rows and one without a slot), on slots in any order; a slot that is cleared
     and used again starts from zeros."""
     from kvforge_b200 import ops
 
-    dev, dt = "cuda", DT[dtype]
-    c = 40
+    dev, dt = "cuda", DT[dtype]  # 40 channels: 16-byte loads; 30 and 36 (in bfloat16): one channel a thread
     g = torch.Generator().manual_seed(taps)
     w = torch.randn(c, taps, generator=g)
     seqs = [torch.randn(n, c, generator=g).to(dt).float() for n in (23, 9, 14)]
