@@ -155,6 +155,78 @@ __global__ void __launch_bounds__(128) causal_conv_kernel(const T* __restrict__ 
   }
 }
 
+// Steps in which no sequence brings more than CONV_FEW rows (decoding): a thread owns VEC channels of ALL rows of
+// one sequence, so it reads the old state, computes the rows and writes the new state itself: one launch.
+constexpr int CONV_FEW = 4;
+
+template <typename T, int VEC, int TAPS>
+__global__ void __launch_bounds__(128) causal_conv_few_kernel(const T* __restrict__ x, int x_stride, const float* __restrict__ w,
+                                                              float* __restrict__ state, long long state_stride,
+                                                              const int* __restrict__ qsl, const int* __restrict__ state_slots,
+                                                              int C, int act, T* __restrict__ out, int out_stride) {
+  pdl_launch();
+  pdl_wait();
+  const int b = blockIdx.x;
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * VEC;
+  const int first = qsl[b], q_len = qsl[b + 1] - first;
+  const int slot = state_slots[b];
+  if (c >= C || q_len <= 0 || q_len > CONV_FEW) return;
+  float* st = slot >= 0 ? state + (size_t)slot * state_stride : nullptr;
+  float wr[VEC][TAPS];
+#pragma unroll
+  for (int e = 0; e < VEC; ++e)
+#pragma unroll
+    for (int j = 0; j < TAPS; ++j) wr[e][j] = w[(size_t)(c + e) * TAPS + j];
+  float u[TAPS - 1 + CONV_FEW][VEC];  // the state's inputs, then this step's rows
+#pragma unroll
+  for (int i = 0; i < TAPS - 1; ++i)
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) u[i][e] = st ? st[(size_t)i * C + c + e] : 0.f;
+#pragma unroll
+  for (int i = 0; i < CONV_FEW; ++i) {
+    if (i < q_len) VecIO<T, VEC>::load(x + (size_t)(first + i) * x_stride + c, u[TAPS - 1 + i]);
+    else
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) u[TAPS - 1 + i][e] = 0.f;
+  }
+#pragma unroll
+  for (int i = 0; i < CONV_FEW; ++i) {
+    if (i < q_len) {
+      float acc[VEC];
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        acc[e] = 0.f;
+#pragma unroll
+        for (int j = 0; j < TAPS; ++j) acc[e] = fmaf(wr[e][j], u[i + j][e], acc[e]);
+        if (act == 1) acc[e] = silu_f(acc[e]);
+      }
+      VecIO<T, VEC>::store(out + (size_t)(first + i) * out_stride + c, acc);
+    }
+  }
+  if (st) {  // the last TAPS-1 inputs, oldest first
+#pragma unroll
+    for (int i = 0; i < TAPS - 1; ++i) {
+#pragma unroll
+      for (int k = 0; k < TAPS - 1 + CONV_FEW; ++k)
+        if (k == q_len + i) {
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) st[(size_t)i * C + c + e] = u[k][e];
+        }
+    }
+  }
+}
+
+template <typename T, int VEC>
+int launch_conv_few(const T* x, int x_stride, const float* w, float* state, long long state_stride, const int* qsl,
+                    const int* state_slots, int B, int C, int taps, int act, T* out, int out_stride, cudaStream_t st) {
+  const int per_cta = 128 * VEC;
+  dim3 grid(B, (C + per_cta - 1) / per_cta);
+  if (grid.y > 65535u) return (int)cudaErrorInvalidValue;
+  if (taps == 2) return launch(causal_conv_few_kernel<T, VEC, 2>, grid, dim3(128), 0, st, x, x_stride, w, state, state_stride, qsl, state_slots, C, act, out, out_stride);
+  if (taps == 3) return launch(causal_conv_few_kernel<T, VEC, 3>, grid, dim3(128), 0, st, x, x_stride, w, state, state_stride, qsl, state_slots, C, act, out, out_stride);
+  return launch(causal_conv_few_kernel<T, VEC, 4>, grid, dim3(128), 0, st, x, x_stride, w, state, state_stride, qsl, state_slots, C, act, out, out_stride);
+}
+
 template <typename T, int VEC>
 int launch_conv(const T* x, int x_stride, const float* w, const float* state, long long state_stride, const int* qsl,
                 const int* state_slots, int N, int B, int C, int taps, int act, T* out, int out_stride, cudaStream_t st) {
@@ -253,6 +325,9 @@ struct DeltaParams {
   float* gn;
   float* sc;
   int N;
+  // the logits of beta (and of a per-head step size) may come as the float slices of a split-K product
+  int logit_slices;
+  long long logit_slice_stride;
 };
 
 // exp(rate * softplus(x)), rate < 0: exact library functions in 32-bit storage; in bfloat16 storage the fast
@@ -304,9 +379,15 @@ __global__ void __launch_bounds__(128) delta_prepare_kernel(const DeltaParams p)
   }
   if (lane == 0) {
     float* so = p.sc + ((size_t)n * p.H + h) * 4;
-    so[0] = sigmoid_f(p.b[n * p.b_stride + h]);
+    float bl = p.b[n * p.b_stride + h];
+    float al = p.per_channel ? 0.f : p.a[n * p.a_stride + h];
+    for (int sl = 1; sl < p.logit_slices; ++sl) {  // in slice order
+      bl += p.b[(size_t)sl * p.logit_slice_stride + n * p.b_stride + h];
+      if (!p.per_channel) al += p.a[(size_t)sl * p.logit_slice_stride + n * p.a_stride + h];
+    }
+    so[0] = sigmoid_f(bl);
     so[1] = kq * ik * iq;
-    so[2] = p.per_channel ? 1.f : decay_of<T>(neg_rate, p.a[n * p.a_stride + h] + p.dt_bias[h]);
+    so[2] = p.per_channel ? 1.f : decay_of<T>(neg_rate, al + p.dt_bias[h]);
     so[3] = 0.f;
   }
 }
@@ -603,12 +684,18 @@ __global__ void __launch_bounds__(128) gated_head_norm_kernel(const float* __res
 #define KVF_SEQMIX_API(SUF, T)                                                                                        \
   KVF_API int kvf_causal_conv_##SUF(const void* x, int x_stride, const float* w, float* state, long long state_stride, \
                                     const int* qsl, const int* state_slots, int N, int B, int C, int taps, int act,    \
-                                    void* out, int out_stride, cudaStream_t st) {                                      \
+                                    void* out, int out_stride, int max_q_len, cudaStream_t st) {                       \
     if (N <= 0 || B <= 0 || C <= 0) return 0;                                                                          \
     if (taps <= 0 || (unsigned)B > 65535u) return (int)cudaErrorInvalidValue;                                          \
     constexpr int V = ConvVec<T>::N;                                                                                   \
     const bool vec = C % V == 0 && x_stride % V == 0 && out_stride % V == 0 && ((uintptr_t)x % 16) == 0 &&             \
                      ((uintptr_t)out % 16) == 0;                                                                       \
+    if (max_q_len > 0 && max_q_len <= CONV_FEW && taps >= 2 && taps <= 4) {                                            \
+      return vec ? launch_conv_few<T, V>((const T*)x, x_stride, w, state, state_stride, qsl, state_slots, B, C, taps,  \
+                                         act, (T*)out, out_stride, st)                                                 \
+                 : launch_conv_few<T, 1>((const T*)x, x_stride, w, state, state_stride, qsl, state_slots, B, C, taps,  \
+                                         act, (T*)out, out_stride, st);                                                \
+    }                                                                                                                  \
     int rc = vec ? launch_conv<T, V>((const T*)x, x_stride, w, state, state_stride, qsl, state_slots, N, B, C, taps,   \
                                      act, (T*)out, out_stride, st)                                                     \
                  : launch_conv<T, 1>((const T*)x, x_stride, w, state, state_stride, qsl, state_slots, N, B, C, taps,   \
@@ -625,7 +712,8 @@ __global__ void __launch_bounds__(128) gated_head_norm_kernel(const float* __res
                                     const float* dt_bias, int per_channel, float* state, long long state_stride,       \
                                     float* out, int out_stride, const int* qsl, const int* state_slots, int B, int H,  \
                                     int G, int dk, int dv, float q_scale, float norm_eps, int max_q_len, int N,        \
-                                    float* kn, float* qn, float* gn, float* sc, cudaStream_t st) {                     \
+                                    float* kn, float* qn, float* gn, float* sc, int logit_slices,                      \
+                                    long long logit_slice_stride, cudaStream_t st) {                                   \
     if (B <= 0) return 0;                                                                                              \
     if (H <= 0 || G <= 0 || H % G || dk <= 0 || dv <= 0 || (unsigned)H > 65535u) return (int)cudaErrorInvalidValue;    \
     DeltaParams p;                                                                                                     \
@@ -634,6 +722,7 @@ __global__ void __launch_bounds__(128) gated_head_norm_kernel(const float* __res
     p.state_stride = state_stride; p.out = out; p.out_stride = out_stride; p.qsl = qsl; p.state_slots = state_slots;   \
     p.H = H; p.G = G; p.dk = dk; p.dv = dv; p.q_scale = q_scale; p.norm_eps = norm_eps; p.chunk = 1; p.buf_floats = 0;  \
     p.kn = kn; p.qn = qn; p.gn = gn; p.sc = sc; p.N = N;                                                               \
+    p.logit_slices = logit_slices; p.logit_slice_stride = logit_slice_stride;                                          \
     if (!kn || !qn || !sc || (per_channel && !gn)) return (int)cudaErrorInvalidValue;                                  \
     return dispatch_delta<T>(p, B, max_q_len, st);                                                                     \
   }                                                                                                                    \

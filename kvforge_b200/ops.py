@@ -36,8 +36,8 @@ _SIGNATURES = {
     "kvf_sample_f32": "pliippppppp",
     "kvf_argmax_f32": "pliipipp",
     # library "mixers"
-    "kvf_causal_conv_{s}": "pipplppiiiiipip",
-    "kvf_gated_delta_{s}": "pppipipippiplpippiiiiiffiippppp",
+    "kvf_causal_conv_{s}": "pipplppiiiiipiip",
+    "kvf_gated_delta_{s}": "pppipipippiplpippiiiiiffiippppilp",
     "kvf_gated_head_norm_{s}": "pipipfiliipip",
     "kvf_hc_step_{s}": "pppilppppppiiifp",
     "kvf_branch_norm_mean_{s}": "pppppilifpp",
@@ -943,7 +943,7 @@ def _state_view(state: torch.Tensor, width: int, what: str) -> tuple[int, int]:
 
 def causal_conv(
     x: torch.Tensor, weight: torch.Tensor, state: torch.Tensor, qsl: torch.Tensor, state_slots: torch.Tensor,
-    num_seqs: int, out: torch.Tensor, activation: str | None = None,
+    num_seqs: int, out: torch.Tensor, activation: str | None = None, max_query_len: int = 0,
 ) -> None:  # fmt: skip
     """Short causal convolution over time per channel of a flat batch, and the state moved on.
 
@@ -951,7 +951,8 @@ def causal_conv(
     column multiplies the current token, ``state`` float ``[slots, (taps-1)*C]``: the last
     ``taps-1`` inputs of each sequence, oldest first, zeros before its start.  ``out [N, C]`` gets
     the sums (``activation``: ``None`` or ``"silu"``); afterwards the state holds this step's last
-    inputs.  Sequences without rows and slots below zero are left alone."""
+    inputs.  Sequences without rows and slots below zero are left alone.  ``max_query_len`` (0 =
+    unknown): the most rows a sequence brings; up to 4 (with 2 to 4 taps) one kernel does both."""
     s = _suffix(x.dtype)
     _rows2d(x, None, "x")
     _rows2d(out, x.dtype, "out")
@@ -969,10 +970,10 @@ def causal_conv(
     _check(
         _fn(name, MIXERS_LIB)(
             _ptr(x), x.stride(0), _ptr(weight), sptr, sstride, _ptr(qsl), _ptr(state_slots), n, num_seqs, c, taps,
-            1 if activation == "silu" else 0, _ptr(out), out.stride(0), _stream(),
+            1 if activation == "silu" else 0, _ptr(out), out.stride(0), int(max_query_len), _stream(),
         ),
         name,
-        1 if taps == 1 else 2,
+        1 if taps == 1 or (0 < max_query_len <= 4 and 2 <= taps <= 4) else 2,
     )  # fmt: skip
 
 
@@ -981,6 +982,7 @@ def gated_delta(
     a_log: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor, out: torch.Tensor, qsl: torch.Tensor,
     state_slots: torch.Tensor, num_seqs: int, num_heads: int, num_kv_heads: int, dk: int, dv: int, q_scale: float,
     norm_eps: float = 1e-6, max_query_len: int = 0, scratch: tuple[torch.Tensor, ...] | None = None,
+    logit_slices: int = 0, logit_slice_stride: int = 0,
 ) -> None:  # fmt: skip
     """The gated delta rule over a flat batch, token by token per sequence, on the state
     ``S [heads, dk, dv]`` of each sequence's slot (``csrc/sequence_mix.cu`` has the equations).
@@ -992,7 +994,9 @@ def gated_delta(
     sequence of the step brings; up to 4 the kernel takes the form made for steps of single tokens.
     ``scratch``: float buffers ``(kn [N, H*dk], qn [N, H*dk], gn [N, H*dk] or None, sc [N, H*4])`` for what
     a kernel of its own makes of every token before the walk (unit k and q, decays, beta, k.q); without it
-    they are allocated here (tests; a step of the engine passes persistent buffers).  Two launches."""
+    they are allocated here (tests; a step of the engine passes persistent buffers).  Two launches.
+    ``logit_slices > 1``: ``beta_logits`` (and per-head ``step_logits``) are slice 0 of that many float
+    slices of a split-K product, ``logit_slice_stride`` elements apart, summed in slice order."""
     s = _suffix(q.dtype)
     h, g = int(num_heads), int(num_kv_heads)
     for t, w, what in ((q, g * dk, "q"), (k, g * dk, "k"), (v, h * dv, "v")):
@@ -1029,7 +1033,7 @@ def gated_delta(
             _ptr(q), _ptr(k), _ptr(v), q.stride(0), _ptr(beta_logits), beta_logits.stride(0), _ptr(step_logits),
             step_logits.stride(0), _ptr(a_log), _ptr(dt_bias), 1 if per_channel else 0, sptr, sstride, _ptr(out),
             out.stride(0), _ptr(qsl), _ptr(state_slots), num_seqs, h, g, dk, dv, float(q_scale), float(norm_eps), int(max_query_len),
-            n, _ptr(kn), _ptr(qn), _ptr(gn) if per_channel else None, _ptr(sc), _stream(),
+            n, _ptr(kn), _ptr(qn), _ptr(gn) if per_channel else None, _ptr(sc), int(logit_slices), int(logit_slice_stride), _stream(),
         ),
         name,
         2,

@@ -182,7 +182,7 @@ class PagedAttention(Mixer):
             ops.linear(x, self.w_qkv, qkv)
         if self.taps:
             mixed = rt.buf("attn.qkv_conv", n, self.qkv_dim)
-            ops.causal_conv(qkv, self.w_conv, cache.state, ctx.query_start_loc, ctx.state_slots, ctx.num_seqs, mixed)
+            ops.causal_conv(qkv, self.w_conv, cache.state, ctx.query_start_loc, ctx.state_slots, ctx.num_seqs, mixed, max_query_len=ctx.max_query_len)
             qkv = mixed
         ops.rope_cache_general(
             qkv, ctx.positions, self.inv_freq, self.interleaved, ctx.slot_mappings[cache.group], cache.k, cache.v,

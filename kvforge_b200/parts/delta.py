@@ -147,11 +147,24 @@ class GatedDeltaRule(Mixer):
         H, dk, dv = self.H, self.dk, self.dv
         main = rt.buf("delta.main", n, self.w_main.shape[0])
         product(x, self.w_main, main)
-        small = rt.buf("delta.small", n, self.w_small.shape[0], torch.float32)
-        product(x, self.w_small, small)
+        # the logits of beta (and of a per-head step size): few output rows, so for a few tokens the product runs over
+        # slices of K in parallel and the kernel that prepares the delta rule's inputs sums the slices
+        c_small = self.w_small.shape[0]
+        slices = ops.skinny_splits(c_small, self.hidden, n) if (ops.skinny_ok(x, self.w_small) and n <= 8) else 1
+        slices = min(slices, 8)
+        if slices > 1:
+            part = rt.buf("delta.small_part", 8 * 8, c_small, torch.float32, cap=64)[: slices * n].view(slices, n, c_small)
+            ops.gemm_skinny(x, self.w_small, ops.Partials(part))
+            small, slice_stride = part[0], part.stride(0)
+        else:
+            small, slice_stride = rt.buf("delta.small", n, c_small, torch.float32), 0
+            product(x, self.w_small, small)
         qkv = rt.buf("delta.qkv", n, self.c_qkv)
         conv_state = cache.state[:, : self.conv_floats]
-        ops.causal_conv(main[:, : self.c_qkv], self.w_conv, conv_state, ctx.query_start_loc, ctx.state_slots, ctx.num_seqs, qkv, activation="silu")
+        ops.causal_conv(
+            main[:, : self.c_qkv], self.w_conv, conv_state, ctx.query_start_loc, ctx.state_slots, ctx.num_seqs, qkv, activation="silu",
+            max_query_len=ctx.max_query_len,
+        )
         if self.decay_rank:
             r = int(self.decay_rank)
             step = rt.buf("delta.step", n, self.a_width, torch.float32)
@@ -174,6 +187,7 @@ class GatedDeltaRule(Mixer):
             qkv[:, : self.c_q], qkv[:, self.c_q : 2 * self.c_q], qkv[:, 2 * self.c_q :], small[:, :H], step, self.a_log, self.dt_bias,
             cache.state[:, self.conv_floats :], read, ctx.query_start_loc, ctx.state_slots, ctx.num_seqs, H, self.G, dk, dv,
             q_scale=dk**-0.5, norm_eps=1e-6, max_query_len=ctx.max_query_len, scratch=scratch,
+            logit_slices=slices if slices > 1 else 0, logit_slice_stride=slice_stride,
         )  # fmt: skip
         y = rt.buf("delta.y", n, self.c_v)
         ops.gated_head_norm(read, gate, self.norm_w, self.eps, y, H, dv, activation=self.gate)

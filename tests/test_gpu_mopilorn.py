@@ -274,7 +274,7 @@ def test_short_convolution_with_state(dtype, taps, act, c):
         want = [F.silu(y) for y in want]
     state = torch.zeros(6, 7 + (taps - 1) * c, device=dev)  # the mixer's columns start at 7
     view = state[:, 7:]
-    cuts = [[5, 1, 0, 2, 15], [2, 3, 4, 0, 0], [1, 1, 1, 8, 3]]
+    cuts = [[5, 1, 0, 2, 15], [2, 3, 4, 0, 0], [1, 1, 1, 8, 3]]  # steps 1 and 2 bring at most four rows a sequence
     slots = [4, 0, 2]
     got = [[] for _ in seqs]
     at = [0, 0, 0]
@@ -284,7 +284,7 @@ def test_short_convolution_with_state(dtype, taps, act, c):
         x = torch.cat([seqs[i][at[i] : at[i] + lens[i]] for i in range(3)] + [torch.randn(3, c, generator=g)]).to(dev, dt)
         qsl, sl = flat_batch(lens + [0, 0], slots + [5, -1], dev)
         out = torch.full_like(x, 7.0)
-        ops.causal_conv(x, w.to(dev), view, qsl, sl, 5, out, activation=act)
+        ops.causal_conv(x, w.to(dev), view, qsl, sl, 5, out, activation=act, max_query_len=max(lens) if step in (1, 2) else 0)
         assert bool((out[-3:] == 7.0).all())
         o = 0
         for i in range(3):
@@ -367,9 +367,17 @@ def test_gated_delta_rule_through_the_state(dtype, h, g, dk, dv, channel):
         b, a = cat(1).to(dev), cat(2).to(dev)
         qsl, sl = flat_batch(ls, [2, 0], dev)
         out = torch.empty(sum(ls), h * dv, device=dev)
+        extra = {}
+        if step % 2 == 1 and not channel:
+            # the logits as three float slices that sum to them (what a product over slices of K leaves)
+            both = torch.cat([b, a], dim=1)
+            parts = torch.randn(3, *both.shape, device=dev)
+            parts[0] = both - parts[1] - parts[2]
+            b, a = parts[0][:, :h], parts[0][:, h:]
+            extra = dict(logit_slices=3, logit_slice_stride=parts.stride(0))
         ops.gated_delta(
             qkv[:, : g * dk], qkv[:, g * dk : 2 * g * dk], qkv[:, 2 * g * dk :], b, a, a_log.to(dev), dt_bias.to(dev), state[:, 5:], out,
-            qsl, sl, 2, h, g, dk, dv, q_scale=dk**-0.5,
+            qsl, sl, 2, h, g, dk, dv, q_scale=dk**-0.5, max_query_len=max(ls) if step >= 2 else 0, **extra,
         )  # fmt: skip
         o = 0
         for i in range(2):
