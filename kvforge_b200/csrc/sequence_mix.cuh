@@ -12,6 +12,7 @@
 // itself) is float whatever the storage type T is.  Every sum has a fixed order that depends on the
 // sizes alone, so a token's result does not depend on how its sequence was cut into steps or on what
 // else the step holds.
+#pragma once
 #include "common.cuh"
 
 using namespace kvf;
@@ -738,5 +739,3 @@ __global__ void __launch_bounds__(128) gated_head_norm_kernel(const float* __res
     return KVF_LAUNCH_STATUS();                                                                                        \
   }
 
-KVF_SEQMIX_API(f32, float)
-KVF_SEQMIX_API(bf16, bf16)

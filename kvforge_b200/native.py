@@ -38,7 +38,7 @@ LIBRARIES: dict[str, tuple[list[str], list[str]]] = {
     "noalloc": (["attention_decode_noalloc.cu"], []),
     # what mixers with a running state, several residual streams and the general rotary form need; a
     # library of its own, so that a model without them never compiles it
-    "mixers": (["sequence_mix.cu", "streams.cu"], []),
+    "mixers": (["sequence_mix_f32.cu", "sequence_mix_bf16.cu", "streams.cu"], []),
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

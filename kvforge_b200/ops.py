@@ -985,7 +985,7 @@ def gated_delta(
     logit_slices: int = 0, logit_slice_stride: int = 0,
 ) -> None:  # fmt: skip
     """The gated delta rule over a flat batch, token by token per sequence, on the state
-    ``S [heads, dk, dv]`` of each sequence's slot (``csrc/sequence_mix.cu`` has the equations).
+    ``S [heads, dk, dv]`` of each sequence's slot (``csrc/sequence_mix.cuh`` has the equations).
 
     ``q, k [N, G*dk]`` and ``v [N, H*dv]`` are column slices of one buffer (same row stride);
     ``beta_logits`` float ``[N, H]``; ``step_logits`` float ``[N, H]`` (one decay a head) or
