@@ -12,6 +12,8 @@ Added: cache *groups*.  Layers that keep the same thing per token form a group w
 and tables of its own.  A ``full`` group keeps every key.  A ``window`` group keeps the last
 ``window`` keys: ``append_slots`` gives pages back once every position in them lies before
 ``write_start - window + 1`` (no later query can see them); the table entry becomes ``-1``.
+A window group may also keep the first ``keep_first`` positions of every request for good
+(queries see them at any distance): the pages that hold them are never given back.
 """
 
 from __future__ import annotations
@@ -33,12 +35,15 @@ RELEASED = -1
 class GroupSpec:
     kind: str = "full"  # "full" or "window"
     window: int | None = None
+    keep_first: int = 0  # window groups: the first positions of a request stay visible, so their pages stay
 
     def __post_init__(self) -> None:
         if self.kind not in ("full", "window"):
             raise ValueError(f"cache group kind {self.kind!r} is not 'full' or 'window'")
         if self.kind == "window" and (self.window is None or self.window <= 0):
             raise ValueError("a window group needs a positive window")
+        if self.keep_first < 0 or (self.keep_first and self.kind != "window"):
+            raise ValueError("keep_first is a count of positions of a window group")
 
 
 @dataclass(frozen=True)
@@ -145,6 +150,10 @@ class BlockManager:
             return 0
         return max(0, write_start - pool.spec.window + 1) // self.block_size
 
+    def _kept_blocks(self, pool: _Pool) -> int:
+        """Pages at the start of a request that a window group never gives back."""
+        return self.blocks_needed(pool.spec.keep_first) if pool.spec.kind == "window" else 0
+
     def _demand(self, pool: _Pool, seq_id: str | None, total_tokens: int, write_start: int) -> tuple[int, int]:
         """(pages to take, pages that come back first) for holding ``total_tokens`` tokens
         when writing starts at ``write_start``."""
@@ -153,8 +162,10 @@ class BlockManager:
         if pool.spec.kind != "window":
             return max(0, want - len(table)), 0  # a full group never gives pages back: no holes in its table
         first = self._first_live_block(pool, write_start)
-        take = sum(1 for i in range(first, want) if i >= len(table) or table[i] < 0)
-        back = sum(1 for i in range(min(first, len(table))) if table[i] >= 0)
+        kept = min(self._kept_blocks(pool), first)
+        live = [i for i in range(want) if i < kept or i >= first]
+        take = sum(1 for i in live if i >= len(table) or table[i] < 0)
+        back = sum(1 for i in range(kept, min(first, len(table))) if table[i] >= 0)
         return take, back
 
     def can_ever_fit(self, num_tokens: int, max_portion: int) -> bool:
@@ -163,7 +174,7 @@ class BlockManager:
         for pool in self._pools:
             need = self.blocks_needed(num_tokens)
             if pool.spec.kind == "window":
-                need = min(need, self.blocks_needed(pool.spec.window - 1 + max_portion) + 1)
+                need = min(need, self.blocks_needed(pool.spec.window - 1 + max_portion) + 1 + self._kept_blocks(pool))
             if need > pool.num_blocks - self.watermark_blocks:
                 return False
         return True
@@ -221,13 +232,14 @@ class BlockManager:
                     table.append(pool.pop())
                 continue
             first = self._first_live_block(pool, write_start)
-            for i in range(min(first, len(table))):
+            kept = min(self._kept_blocks(pool), first)
+            for i in range(kept, min(first, len(table))):
                 if table[i] >= 0:
                     pool.release(table[i])
                     table[i] = RELEASED
             while len(table) < want:
-                table.append(RELEASED if len(table) < first else pool.pop())
-            for i in range(first, want):
+                table.append(RELEASED if kept <= len(table) < first else pool.pop())
+            for i in [*range(min(kept, want)), *range(first, want)]:
                 if table[i] < 0:
                     table[i] = pool.pop()
         self._num_tokens[seq_id] = max(self._num_tokens[seq_id], total_tokens)

@@ -23,7 +23,8 @@ class KVPool:
         for g in model.groups:
             shape = (len(g.calls), num_blocks, g.need.kv_heads, block_size)
             self.k.append(torch.zeros((*shape, g.need.head_dim), dtype=dtype, device=device))
-            self.v.append(torch.zeros((*shape, g.need.value_dim), dtype=dtype, device=device))
+            # values that are the leading part of the keys (a latent shared by keys and values) have no tensor of their own
+            self.v.append(self.k[-1] if g.need.v_in_k else torch.zeros((*shape, g.need.value_dim), dtype=dtype, device=device))
         self.states: list[torch.Tensor | None] = []
         for shape in model.state_shapes:
             self.states.append(None if shape is None else torch.zeros((num_slots, *shape), dtype=torch.float32, device=device))
@@ -39,7 +40,7 @@ class KVPool:
 
     @property
     def memory_bytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in self.k + self.v)
+        return sum(t.numel() * t.element_size() for t in self.k + [v for k, v in zip(self.k, self.v) if v is not k])
 
     @property
     def bytes_per_block(self) -> int:
@@ -57,4 +58,4 @@ def bytes_per_block(model, block_size: int, dtype: torch.dtype) -> int:
     """Bytes that one page index costs over all groups and entries, keys and values
     (src/tokenvault/config.py:91-95 for a single group)."""
     elem = torch.tensor([], dtype=dtype).element_size()
-    return sum(len(g.calls) * block_size * g.need.kv_heads * (g.need.head_dim + g.need.value_dim) * elem for g in model.groups)
+    return sum(len(g.calls) * block_size * g.need.kv_heads * (g.need.head_dim + (0 if g.need.v_in_k else g.need.value_dim)) * elem for g in model.groups)

@@ -68,6 +68,11 @@ def _ensure_builtin() -> None:
 
     if ARCHITECTURE not in ARCHITECTURES:
         register_architecture(ARCHITECTURE, MopilornConfig.from_dict, mopilorn_spec, needs_tensor_shapes=True)
+    from ..models.setenex import setenex_spec
+    from .setenex_config import ARCHITECTURE as SETENEX, SetenexConfig
+
+    if SETENEX not in ARCHITECTURES:
+        register_architecture(SETENEX, SetenexConfig.from_dict, setenex_spec, needs_tensor_shapes=True)
 
 
 _LLAMA3_32 = RopeScaling(factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0, original_max_position_embeddings=8192)
@@ -108,3 +113,7 @@ PRESETS["llama-8b"] = PRESETS["llama-3.1-8b"]
 from .mopilorn_config import MOPILORN_PRESETS  # noqa: E402
 
 PRESETS.update(MOPILORN_PRESETS)
+
+from .setenex_config import SETENEX_PRESETS  # noqa: E402
+
+PRESETS.update(SETENEX_PRESETS)

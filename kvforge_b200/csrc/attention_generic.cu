@@ -1,13 +1,15 @@
 // Paged grouped-query attention over block tables on the FP32 pipes, for any head size
-// (a multiple of 8, at most 256), any number of heads and groups, and any mix of
+// (a multiple of 8; keys at most 1024 wide, values at most 512), any number of heads and groups, and any mix of
 // query lengths in one flat batch.  This is the attention of the true 32-bit path and
 // the fall-back of the bfloat16 path for head sizes that have no tensor-core kernel.
 //
 // Contract (what every attention kernel of this engine computes): sequence b has
 // ctx_b keys in its pages after this step's writes and q_b = qsl[b+1]-qsl[b] queries;
 // query i sits at position p = ctx_b - q_b + i and sees key j iff j <= p (and
-// j > p - window when window > 0).  S = scale * (q . k) in float, softmax in float,
-// O = P V in float, one rounding to T.
+// j > p - window when window > 0, or j < keep_first: the first keys of a sequence may stay
+// visible at any distance).  S = scale * (q . k) in float, plus, when a table is given, a learned
+// bias by distance: bias[bucket[min(p - j, far)]][head], with `bucket` an int table of far + 1
+// entries and `bias` float [rows][nh]; softmax in float, O = P V in float, one rounding to T.
 //
 // Exactness: keys are walked in tiles of 32 that start at absolute positions (multiples
 // of 32), each score is one thread's sequential dot product, and a fully masked tile
@@ -15,7 +17,9 @@
 // prompt was cut, on the other rows of its tile, or on the physical pages.
 //
 // Cache layout per layer: K [num_blocks][nkv][block_size][d] and V [num_blocks][nkv][block_size][dv]
-// (values may have a size of their own; the output rows then hold nh heads of dv).
+// (values may have a size of their own; the output rows then hold nh heads of dv).  A value row may
+// lie inside its key row (vcache == kcache, v_stride == d: the value is the key's first dv numbers,
+// the latent that keys and values share); the key tile in shared memory then serves as value tile.
 #include "common.cuh"
 
 using namespace kvf;
@@ -40,7 +44,11 @@ struct AttnParams {
   int q_stride, out_stride, bt_stride;
   int nh, nkv, d, dv, block_size;
   int gh, chunks, tq;  // heads per CTA, head chunks per kv head, tokens per CTA
-  int window;
+  int window, keep_first;
+  int v_stride;           // elements between the value rows of neighbouring keys in a page
+  const float* bias;      // [rows][nh] or null
+  const int* bias_bucket; // [bias_far + 1]: row of `bias` for a distance
+  int bias_far;
   int split_size, max_splits;
   float scale;
 };
@@ -68,10 +76,11 @@ template <typename T, int DPL, bool SPLIT>
 __global__ void __launch_bounds__(WARPS * 32) paged_attn_generic_kernel(const AttnParams p) {
   extern __shared__ __align__(16) float smem[];
   const int d = p.d, ldk = d + 4;
-  const int dv = p.dv, ldv = dv + 4;
-  float* Ks = smem;                    // [TK][ldk]
-  float* Vs = Ks + TK * ldk;           // [TK][ldv]
-  float* Qs = Vs + TK * ldv;           // [ROWS][d]
+  const bool v_in_k = (p.vcache == p.kcache);
+  const int dv = p.dv, ldv = v_in_k ? ldk : dv + 4;
+  float* Ks = smem;                                 // [TK][ldk]
+  float* Vs = v_in_k ? Ks : Ks + TK * ldk;          // [TK][ldv]
+  float* Qs = v_in_k ? Ks + TK * ldk : Vs + TK * ldv;  // [ROWS][d]
   float* Ps = Qs + ROWS * d;           // [WARPS][RPW][TK]
 
   const int b = blockIdx.y;
@@ -83,13 +92,14 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attn_generic_kernel(const At
   if (q_len <= 0 || ctx <= 0) return;
 
   int q0, kv_lo, kv_hi;  // first query token of this CTA; key range [kv_lo, kv_hi)
+  int win_lo = 0;        // first tile that may hold a key inside the window of this CTA's first query
   if (SPLIT) {
     q0 = q_len - 1;  // one query per sequence (the last, if a caller passes more)
     kv_lo = blockIdx.x * p.split_size;
     if (kv_lo >= ctx) return;  // a range past the context: the merge never reads it
     kv_hi = min(ctx, kv_lo + p.split_size);
-    if (p.window > 0) kv_lo = max(kv_lo, ((max(0, ctx - p.window)) / TK) * TK);
-    if (kv_lo >= kv_hi) {
+    if (p.window > 0) win_lo = ((max(0, ctx - p.window)) / TK) * TK;
+    if (p.window > 0 && kv_hi <= win_lo && kv_lo >= p.keep_first) {
       // a range that lies wholly before the window is empty, and says so to the merge
       for (int r = threadIdx.x; r < p.gh; r += blockDim.x) {
         const int head = kvh * g + chunk * p.gh + r;
@@ -107,7 +117,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attn_generic_kernel(const At
     const int p_first = ctx - q_len + q0;
     const int p_last = ctx - q_len + min(q0 + p.tq, q_len) - 1;
     kv_lo = 0;
-    if (p.window > 0) kv_lo = (max(0, p_first - p.window + 1) / TK) * TK;
+    if (p.window > 0) win_lo = (max(0, p_first - p.window + 1) / TK) * TK;
     kv_hi = p_last + 1;
   }
   const int n_tok = SPLIT ? 1 : min(p.tq, q_len - q0);
@@ -125,13 +135,14 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attn_generic_kernel(const At
 
   // per-row state; row of (warp, slot i) is r = i * WARPS + warp
   float m[RPW], l[RPW], acc[RPW][DPL];
-  int pos[RPW];
+  int pos[RPW], hd[RPW];
 #pragma unroll
   for (int i = 0; i < RPW; ++i) {
     const int r = i * WARPS + warp;
     const int tok = r / p.gh, hh = chunk * p.gh + (r - tok * p.gh);
     const bool valid = (tok < n_tok) && (hh < g);
     pos[i] = valid ? (ctx - q_len + q0 + tok) : -1;  // -1: sees nothing
+    hd[i] = kvh * g + hh;
     m[i] = -INFINITY;
     l[i] = 0.f;
 #pragma unroll
@@ -142,9 +153,14 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attn_generic_kernel(const At
   const T* vc = (const T*)p.vcache;
   const int* bt = p.block_tables + (size_t)b * p.bt_stride;
   constexpr int VN = Vec<T>::N;
-  const int vec_per_row = d / VN, vvec_per_row = dv / VN;
+  const int vec_per_row = d / VN, vvec_per_row = v_in_k ? 0 : dv / VN;
 
   for (int t0 = kv_lo; t0 < kv_hi; t0 += TK) {
+    // tiles between the kept first keys and the window hold nothing any query of this CTA sees
+    if (p.window > 0 && t0 >= p.keep_first && t0 + TK <= win_lo) {
+      t0 = win_lo - TK;
+      continue;
+    }
     __syncthreads();  // previous tile consumed (and Qs staged, first time)
     // ---- load the K and V tile as float; keys >= ctx and released pages are zero-filled
     for (int idx = threadIdx.x; idx < TK * (vec_per_row + vvec_per_row); idx += blockDim.x) {
@@ -157,7 +173,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attn_generic_kernel(const At
       const int blk = kp < ctx ? bt[kp / p.block_size] : -1;
       if (blk >= 0) {  // a page given back (-1) lies wholly outside every window: zeros
         const int off = kp % p.block_size;
-        const size_t base = (((size_t)blk * p.nkv + kvh) * p.block_size + off) * width + c;
+        const size_t base = (((size_t)blk * p.nkv + kvh) * p.block_size + off) * (is_v ? p.v_stride : width) + c;
         load_vec_to_float<T>((is_v ? vc : kc) + base, f);
       } else {
 #pragma unroll
@@ -189,9 +205,13 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attn_generic_kernel(const At
 #pragma unroll
     for (int i = 0; i < RPW; ++i) {
       bool vis = (kp <= pos[i]) && (kp < kv_hi);
-      if (p.window > 0) vis = vis && (kp > pos[i] - p.window);
+      if (p.window > 0) vis = vis && (kp > pos[i] - p.window || kp < p.keep_first);
       if (SPLIT) vis = vis && (kp >= kv_lo);
-      const float sc = vis ? s[i] * p.scale : -INFINITY;
+      float sc = -INFINITY;
+      if (vis) {
+        sc = s[i] * p.scale;
+        if (p.bias) sc += __ldg(p.bias + (size_t)__ldg(p.bias_bucket + min(pos[i] - kp, p.bias_far)) * p.nh + hd[i]);
+      }
       const float tmax = warp_max(sc);
       const float m_new = fmaxf(m[i], tmax);
       float pj = 0.f, corr = 1.f;
@@ -290,7 +310,7 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_acc, const fl
 
 template <typename T, int DPL, bool SPLIT>
 int launch_generic(const AttnParams& p, dim3 grid, cudaStream_t st) {
-  const size_t smem = (size_t)(TK * (p.d + 4) + TK * (p.dv + 4) + ROWS * p.d + WARPS * RPW * TK) * sizeof(float);
+  const size_t smem = (size_t)(TK * (p.d + 4) + (p.vcache == p.kcache ? 0 : TK * (p.dv + 4)) + ROWS * p.d + WARPS * RPW * TK) * sizeof(float);
   auto kern = paged_attn_generic_kernel<T, DPL, SPLIT>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -305,7 +325,8 @@ int dispatch_dpl(const AttnParams& p, dim3 grid, cudaStream_t st) {
   if (p.dv <= 32) return launch_generic<T, 1, SPLIT>(p, grid, st);
   if (p.dv <= 64) return launch_generic<T, 2, SPLIT>(p, grid, st);
   if (p.dv <= 128) return launch_generic<T, 4, SPLIT>(p, grid, st);
-  return launch_generic<T, 8, SPLIT>(p, grid, st);
+  if (p.dv <= 256) return launch_generic<T, 8, SPLIT>(p, grid, st);
+  return launch_generic<T, 16, SPLIT>(p, grid, st);
 }
 
 template <typename T>
@@ -313,11 +334,16 @@ int paged_attention_generic(const void* q, void* out, const void* kcache, const 
                             const int* block_tables, const int* qsl, const int* ctx_lens, int B,
                             int max_q_len, int q_stride, int out_stride, int bt_stride, int nh, int nkv,
                             int d, int dv, int block_size, float scale, int window, int split_size, int max_splits,
-                            int grid_splits, float* part_acc, float* part_ml, cudaStream_t st) {
+                            int grid_splits, float* part_acc, float* part_ml, int keep_first, int v_stride,
+                            const float* bias, const int* bias_bucket, int bias_far, cudaStream_t st) {
   if (B <= 0 || max_q_len <= 0) return 0;
   if (dv <= 0) dv = d;
-  if (d <= 0 || d > 256 || (d % 8) != 0 || dv > 256 || (dv % 8) != 0 || nkv <= 0 || nh % nkv != 0 || block_size <= 0)
+  if (v_stride <= 0) v_stride = dv;
+  if (d <= 0 || d > 1024 || (d % 8) != 0 || dv > 512 || (dv % 8) != 0 || nkv <= 0 || nh % nkv != 0 || block_size <= 0)
     return (int)cudaErrorInvalidValue;
+  if (vcache == kcache && (v_stride != d || dv > d)) return (int)cudaErrorInvalidValue;
+  if (bias && (!bias_bucket || bias_far < 0)) return (int)cudaErrorInvalidValue;
+  if (keep_first < 0) return (int)cudaErrorInvalidValue;
   AttnParams p;
   p.q = q; p.out = out; p.kcache = kcache; p.vcache = vcache;
   p.block_tables = block_tables; p.qsl = qsl; p.ctx_lens = ctx_lens;
@@ -329,6 +355,8 @@ int paged_attention_generic(const void* q, void* out, const void* kcache, const 
   p.chunks = (g + p.gh - 1) / p.gh;
   p.tq = ROWS / p.gh;
   p.window = window; p.scale = scale;
+  p.keep_first = window > 0 ? keep_first : 0; p.v_stride = v_stride;
+  p.bias = bias; p.bias_bucket = bias_bucket; p.bias_far = bias_far;
   p.split_size = split_size; p.max_splits = max_splits;
   if ((unsigned)B > 65535u || (unsigned)(nkv * p.chunks) > 65535u) return (int)cudaErrorInvalidValue;
   if (split_size > 0) {
@@ -354,11 +382,12 @@ int paged_attention_generic(const void* q, void* out, const void* kcache, const 
       const void* q, void* out, const void* kcache, const void* vcache, const int* block_tables,          \
       const int* qsl, const int* ctx_lens, int B, int max_q_len, int q_stride, int out_stride,            \
       int bt_stride, int nh, int nkv, int d, int dv, int block_size, float scale, int window,             \
-      int split_size, int max_splits, int grid_splits, float* part_acc, float* part_ml, cudaStream_t st) { \
+      int split_size, int max_splits, int grid_splits, float* part_acc, float* part_ml, int keep_first,   \
+      int v_stride, const float* bias, const int* bias_bucket, int bias_far, cudaStream_t st) {           \
     return paged_attention_generic<T>(q, out, kcache, vcache, block_tables, qsl, ctx_lens, B, max_q_len,  \
                                       q_stride, out_stride, bt_stride, nh, nkv, d, dv, block_size, scale, \
                                       window, split_size, max_splits, grid_splits, part_acc, part_ml,     \
-                                      st);                                                                \
+                                      keep_first, v_stride, bias, bias_bucket, bias_far, st);             \
   }
 
 KVF_ATTN_API(f32, float)

@@ -88,7 +88,7 @@ class EngineCore:
         self.block_size = cache.block_size
         per_block = bytes_per_block(self.model, cache.block_size, self.dtype)
         self.num_blocks = cache.resolve_num_blocks(per_block)
-        groups = [GroupSpec(g.need.kind, g.need.window) for g in self.model.groups] or [GroupSpec()]
+        groups = [GroupSpec(g.need.kind, g.need.window, g.need.keep_first if g.need.kind == "window" else 0) for g in self.model.groups] or [GroupSpec()]
         self.block_manager = BlockManager(self.num_blocks, cache.block_size, cache.watermark, groups)
         self.state_slots = StateSlotPool(max_num_seqs)
         self.pool = KVPool(self.model, self.num_blocks, cache.block_size, max_num_seqs, self.dtype, self.device)

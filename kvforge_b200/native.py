@@ -39,6 +39,9 @@ LIBRARIES: dict[str, tuple[list[str], list[str]]] = {
     # what mixers with a running state, several residual streams and the general rotary form need; a
     # library of its own, so that a model without them never compiles it
     "mixers": (["sequence_mix_f32.cu", "sequence_mix_bf16.cu", "streams.cu"], []),
+    # attention layers with normed heads or latent keys and values, and the feed-forward of routed experts; a
+    # library of its own for the same reason
+    "routed": (["head_ops.cu", "experts.cu"], []),
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

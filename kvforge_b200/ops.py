@@ -18,13 +18,13 @@ _SUF = {torch.float32: "f32", torch.bfloat16: "bf16"}
 
 # p = pointer, i = int, l = long long, f = float
 _SIGNATURES = {
-    "kvf_embed_{s}": "pppppiiipp",
+    "kvf_embed_{s}": "pppppiiifpp",
     "kvf_add_rmsnorm_{s}": "pppilpppiifp",
     "kvf_add_residual_{s}": "pplp",
     "kvf_rope_cache_{s}": "ppilppppppiiiiiilpp",
     "kvf_silu_mul_{s}": "ppliip",
     "kvf_cast_from_float_{s}": "pplp",
-    "kvf_paged_attention_generic_{s}": "pppppppiiiiiiiiiifiiiippp",
+    "kvf_paged_attention_generic_{s}": "pppppppiiiiiiiiiifiiiippiippip",
     "kvf_paged_attention_mma_bf16": "pppppppiiiiiiiiifiiiippp",
     "kvf_paged_attention_tcgen05_bf16": "pppppppiiiiiiiiilfipipp",
     "kvf_paged_attention_decode_fused_bf16": "pppppppiiiiiiiifiiiipppp",
@@ -45,6 +45,15 @@ _SIGNATURES = {
     "kvf_replicate_streams": "ppliip",
     "kvf_softcap_f32": "plfp",
     "kvf_mixers_set_pdl": "i",
+    # library "routed"
+    "kvf_head_norm_cache_{s}": "plpppfpipppiiiiiilpp",
+    "kvf_latent_prepare_{s}": "pliippfpipppiiiiiilpp",
+    "kvf_head_gate_{s}": "pplliip",
+    "kvf_add_row_f32": "pplip",
+    "kvf_moe_route_{s}": "plppiiiiiifppp",
+    "kvf_moe_experts_{s}": "plppppiiiiippppppp",
+    "kvf_moe_max_tiles": "ii",
+    "kvf_routed_set_pdl": "i",
 }
 _CTYPES = {"p": ctypes.c_void_p, "i": ctypes.c_int, "l": ctypes.c_longlong, "f": ctypes.c_float}
 
@@ -71,8 +80,8 @@ def _fn(name: str, lib: str = "core", signature: str | None = None):
         f.argtypes = [_CTYPES[c] for c in sig]
         f.restype = ctypes.c_int
         _bound[key] = f
-        if lib == "mixers" and name != "kvf_mixers_set_pdl":
-            _sync_mixers_pdl()
+        if lib in _PDL_SETTERS and name != _PDL_SETTERS[lib]:
+            _sync_library_pdl()
     return f
 
 
@@ -120,18 +129,23 @@ def set_pdl(enabled: bool) -> None:
     if _pdl_state is not enabled:
         _fn("kvf_set_pdl")(1 if enabled else 0)
         _pdl_state = enabled
-    _sync_mixers_pdl()
+    _sync_library_pdl()
 
 
-_mixers_pdl = None
+# every shared library has a flag of its own; it follows the core's once the library is loaded
+_PDL_SETTERS = {"mixers": "kvf_mixers_set_pdl", "routed": "kvf_routed_set_pdl"}
+_library_pdl: dict[str, bool] = {}
+
+
+def _sync_library_pdl() -> None:
+    for lib, setter in _PDL_SETTERS.items():
+        if lib in native._loaded and _pdl_state is not None and _library_pdl.get(lib) is not _pdl_state:
+            _fn(setter, lib)(1 if _pdl_state else 0)
+            _library_pdl[lib] = _pdl_state
 
 
 def _sync_mixers_pdl() -> None:
-    """The library of the stateful mixers has a flag of its own; it follows the core's once it is loaded."""
-    global _mixers_pdl
-    if "mixers" in native._loaded and _pdl_state is not None and _mixers_pdl is not _pdl_state:
-        _fn("kvf_mixers_set_pdl", "mixers")(1 if _pdl_state else 0)
-        _mixers_pdl = _pdl_state
+    _sync_library_pdl()
 
 
 # Kernels of this library launched so far (library matrix products are not counted).
@@ -171,8 +185,9 @@ def embed(
     err: torch.Tensor | None = None,
     feedback_rows: torch.Tensor | None = None,
     feedback: torch.Tensor | None = None,
+    scale: float = 1.0,
 ) -> None:
-    """``resid[n, :] = float(table[id, :])``; ``ids`` int32 ``[N]``, ``resid`` float ``[N, H]``.
+    """``resid[n, :] = float(table[id, :]) * scale``; ``ids`` int32 ``[N]``, ``resid`` float ``[N, H]``.
     Where ``feedback_rows[n] >= 0`` the id is ``feedback[feedback_rows[n]]`` (a token sampled on
     the device in the step before) instead of ``ids[n]``."""
     s = _suffix(table.dtype)
@@ -188,7 +203,7 @@ def embed(
         if feedback_rows.numel() < n:
             raise ValueError("embed: feedback_rows is too short")
     name = f"kvf_embed_{s}"
-    _check(_fn(name)(_ptr(table), _ptr(ids), _ptr(feedback_rows), _ptr(feedback), _ptr(resid), n, h, table.shape[0], _ptr(err), _stream()), name)
+    _check(_fn(name)(_ptr(table), _ptr(ids), _ptr(feedback_rows), _ptr(feedback), _ptr(resid), n, h, table.shape[0], float(scale), _ptr(err), _stream()), name)
 
 
 def add_rmsnorm(
@@ -433,9 +448,23 @@ def attention_scratch_shapes(max_seqs: int, nh: int, d: int, max_context: int, s
     return (max_seqs, nh, splits, d), (max_seqs, nh, splits, 2)
 
 
-def check_head_dim(d: int) -> None:
-    if d <= 0 or d % 8 != 0 or d > 256:
-        raise ValueError(f"head_dim {d} is not supported: it must be a multiple of 8, at most 256")
+MAX_KEY_DIM = 1024  # what the FP32-pipe attention kernel takes (a latent shared by all heads is this wide)
+MAX_VALUE_DIM = 512
+
+
+def check_head_dim(d: int, most: int = 256) -> None:
+    if d <= 0 or d % 8 != 0 or d > most:
+        raise ValueError(f"head_dim {d} is not supported: it must be a multiple of 8, at most {most}")
+
+
+@dataclass
+class DistanceBias:
+    """A learned bias on attention scores by distance: ``table`` float ``[rows, heads]`` and
+    ``bucket`` int32 ``[far + 1]``, the row for every distance up to ``far`` (farther keys take the
+    row of ``far``)."""
+
+    table: torch.Tensor
+    bucket: torch.Tensor
 
 
 def mma_attention_supported(dtype: torch.dtype, nh: int, nkv: int, d: int, decode_form: bool) -> bool:
@@ -492,13 +521,17 @@ def paged_attention(
     single_only: bool = False,
     wave_target: int = 0,
     dv: int | None = None,
+    keep_first: int = 0,
+    bias: DistanceBias | None = None,
 ) -> None:
     """Paged GQA attention of a flat batch (the contract is at the top of
     ``csrc/attention_generic.cu``).
 
     ``dv``: size of a value head when it differs from ``d`` (``vcache`` is then
     ``[num_blocks, nkv, block_size, dv]`` and ``out`` ``[N, nh*dv]``); only the FP32-pipe kernel
-    takes such a shape.
+    takes such a shape.  So it is with ``vcache is kcache`` (a value is the first ``dv`` numbers of
+    its key), with ``keep_first`` (under a window, the first keys of every sequence stay visible at
+    any distance) and with ``bias`` (added to the scaled scores, by distance and head).
 
     ``q``: rows of ``q_stride`` elements whose first ``nh*d`` are the query heads; ``out``:
     ``[N, nh*d]``.  With ``scratch`` (and every sequence holding one query) the decode form
@@ -517,7 +550,12 @@ def paged_attention(
     context, over all pairs, are at most this many (``attention_wave_target``).
     """
     s = _suffix(q.dtype)
-    check_head_dim(d)
+    special = vcache is kcache or keep_first > 0 or bias is not None or d > 256 or (dv or d) > 256
+    if special:
+        if kernel not in ("auto", "generic"):
+            raise ValueError("only the FP32-pipe attention kernel takes kept first keys, a distance bias, values inside keys or heads wider than 256")
+        kernel = "generic"
+    check_head_dim(d, MAX_KEY_DIM if special else 256)
     _need(q, None, "q")
     _need(out, q.dtype, "out")
     _need(kcache, q.dtype, "kcache")
@@ -526,9 +564,25 @@ def paged_attention(
     _need(qsl, torch.int32, "query_start_loc")
     _need(ctx_lens, torch.int32, "context_lens")
     dv = d if dv is None else int(dv)
-    check_head_dim(dv)
-    if kcache.dim() != 4 or kcache.shape[1] != nkv or kcache.shape[3] != d or tuple(vcache.shape) != (*kcache.shape[:3], dv):
+    check_head_dim(dv, MAX_VALUE_DIM if special else 256)
+    v_stride = dv
+    if vcache is kcache:
+        if dv > d:
+            raise ValueError("paged_attention: values inside keys cannot be wider than the keys")
+        v_stride = d
+    if kcache.dim() != 4 or kcache.shape[1] != nkv or kcache.shape[3] != d or tuple(vcache.shape) != (*kcache.shape[:3], v_stride):
         raise ValueError("paged_attention: cache shapes must be [num_blocks, nkv, block_size, d] and [..., dv]")
+    if special and 4 * (32 * (d + 4) + (0 if vcache is kcache else 32 * (dv + 4)) + 16 * d + 512) > 227 * 1024:
+        raise ValueError(f"paged_attention: heads of {d} and {dv} do not fit the kernel's shared memory")
+    bias_args = (None, None, 0)
+    if bias is not None:
+        _need(bias.table, torch.float32, "bias table")
+        _need(bias.bucket, torch.int32, "bias buckets")
+        if bias.table.dim() != 2 or bias.table.shape[1] != nh or bias.bucket.numel() < 1:
+            raise ValueError("paged_attention: the bias table must be [rows, heads]")
+        bias_args = (_ptr(bias.table), _ptr(bias.bucket), bias.bucket.numel() - 1)
+    if keep_first < 0:
+        raise ValueError("paged_attention: keep_first is a count of keys")
     if dv != d:
         if kernel not in ("auto", "generic"):
             raise ValueError("only the FP32-pipe attention kernel takes a value size of its own")
@@ -622,7 +676,7 @@ def paged_attention(
         _fn(name)(
             _ptr(q), _ptr(out), _ptr(kcache), _ptr(vcache), _ptr(block_tables), _ptr(qsl), _ptr(ctx_lens),
             num_seqs, max_q_len, q_stride, out.shape[-1], bt_stride, nh, nkv, d, *((dv,) if not use_mma else ()), block_size, float(scale),
-            int(window), split, max_splits, grid_splits, _ptr(pa), _ptr(pm), _stream(),
+            int(window), split, max_splits, grid_splits, _ptr(pa), _ptr(pm), *(() if use_mma else (int(keep_first), v_stride, *bias_args)), _stream(),
         ),
         name,
         2 if scratch is not None else 1,
@@ -1223,4 +1277,191 @@ def rope_cache_general(
             dk, dv, rot, 1 if interleaved else 0, block_size, num_slots, _ptr(err), _stream(),
         ),
         name,
+    )  # fmt: skip
+
+
+# ------------------------------------------------------------------ normed heads, latent keys, routed experts (library "routed")
+
+ROUTED_LIB = "routed"
+
+
+def add_row(resid: torch.Tensor, row: torch.Tensor) -> None:
+    """``resid[n, :] += row`` for every row of the float residual stream."""
+    _need(resid, torch.float32, "resid")
+    _need(row, torch.float32, "row")
+    if resid.dim() != 2 or row.numel() != resid.shape[1]:
+        raise ValueError("add_row: the row must be as wide as the stream")
+    name = "kvf_add_row_f32"
+    _check(_fn(name, ROUTED_LIB)(_ptr(resid), _ptr(row), resid.shape[0], resid.shape[1], _stream()), name)
+
+
+def head_norm_cache(
+    qkv: torch.Tensor, positions: torch.Tensor, q_weight: torch.Tensor | None, k_weight: torch.Tensor | None, eps: float,
+    inv_freq: torch.Tensor | None, slots: torch.Tensor | None, kcache: torch.Tensor | None, vcache: torch.Tensor | None,
+    nh: int, nkv: int, dk: int, dv: int, block_size: int, err: torch.Tensor | None = None,
+) -> None:  # fmt: skip
+    """What follows the q/k/v product of an attention layer whose queries and keys are normed per
+    head: rows of ``qkv`` hold ``nh`` query heads and ``nkv`` key heads of ``dk`` and ``nkv`` value heads
+    of ``dv``.  Query and key heads become ``x / sqrt(mean(x^2) + eps) * weight`` (``weight`` float
+    ``[dk]``, shared by the heads; ``None``: left as they are), then their first ``2*len(inv_freq)``
+    dims turn in interleaved pairs (``None``: no rotation); queries in place, keys and values to
+    ``slots`` of ``kcache [blocks, nkv, block_size, dk]`` / ``vcache [..., dv]``."""
+    s = _suffix(qkv.dtype)
+    _rows2d(qkv, None, "qkv")
+    n = qkv.shape[0]
+    if qkv.shape[1] != (nh + nkv) * dk + nkv * dv or dk % 2:
+        raise ValueError("head_norm_cache: qkv width")
+    _need(positions, torch.int32, "positions")
+    for w, what in ((q_weight, "query norm weight"), (k_weight, "key norm weight")):
+        if w is not None:
+            _need(w, torch.float32, what)
+            if w.numel() != dk:
+                raise ValueError(f"head_norm_cache: the {what} must have {dk} entries")
+    rot = 0
+    if inv_freq is not None and inv_freq.numel():
+        _need(inv_freq, torch.float32, "inv_freq")
+        rot = 2 * inv_freq.numel()
+        if rot > dk:
+            raise ValueError("head_norm_cache: more frequencies than dk/2")
+    num_slots = 0
+    if slots is not None:
+        _need(slots, torch.int32, "slots")
+        _need(kcache, qkv.dtype, "kcache")
+        _need(vcache, qkv.dtype, "vcache")
+        if tuple(kcache.shape[1:]) != (nkv, block_size, dk) or tuple(vcache.shape) != (*kcache.shape[:3], dv):
+            raise ValueError("head_norm_cache: cache shapes must be [num_blocks, nkv, block_size, dk] and [..., dv]")
+        num_slots = kcache.shape[0] * block_size
+    name = f"kvf_head_norm_cache_{s}"
+    _check(
+        _fn(name, ROUTED_LIB)(
+            _ptr(qkv), qkv.stride(0), _ptr(positions), _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(inv_freq) if rot else None, rot,
+            _ptr(slots), _ptr(kcache), _ptr(vcache), n, nh, nkv if slots is not None else 0, dk, dv, block_size, num_slots, _ptr(err), _stream(),
+        ),
+        name,
+    )  # fmt: skip
+
+
+def latent_prepare(
+    x: torch.Tensor, q_off: int, c_off: int, positions: torch.Tensor, c_weight: torch.Tensor, eps: float, inv_freq: torch.Tensor | None,
+    slots: torch.Tensor, cache: torch.Tensor, qa: torch.Tensor, nh: int, dk: int, dr: int, rank: int, block_size: int,
+    err: torch.Tensor | None = None,
+) -> None:  # fmt: skip
+    """For an attention layer whose keys and values come from one latent per token.  Rows of ``x`` hold,
+    from column ``q_off``, ``nh`` query heads of ``dk + dr`` and, from ``c_off``, ``rank`` latent numbers and
+    ``dr`` numbers of a key part shared by all heads.  The latent, RMS-normed with ``c_weight``, and the
+    shared key part, turned with the position, go to ``slots`` of ``cache [blocks, 1, block_size, rank + dr]``;
+    every query head's last ``dr`` numbers, turned, go to columns ``rank .. rank + dr`` of its head in
+    ``qa [N, nh * (rank + dr)]``.  Pairs are interleaved; ``inv_freq`` float ``[rot/2]``, ``rot <= dr``."""
+    s = _suffix(x.dtype)
+    _rows2d(x, None, "x")
+    _need(qa, x.dtype, "qa")
+    _need(cache, x.dtype, "cache")
+    _need(positions, torch.int32, "positions")
+    _need(slots, torch.int32, "slots")
+    _need(c_weight, torch.float32, "latent norm weight")
+    n = x.shape[0]
+    if q_off + nh * (dk + dr) > x.shape[1] or c_off + rank + dr > x.shape[1] or c_weight.numel() != rank or dr % 2:
+        raise ValueError("latent_prepare: the columns do not fit the rows")
+    if tuple(qa.shape) != (n, nh * (rank + dr)) or tuple(cache.shape[1:]) != (1, block_size, rank + dr):
+        raise ValueError("latent_prepare: qa must be [N, nh*(rank+dr)] and the cache [blocks, 1, block_size, rank+dr]")
+    rot = 0
+    if inv_freq is not None and inv_freq.numel():
+        _need(inv_freq, torch.float32, "inv_freq")
+        rot = 2 * inv_freq.numel()
+        if rot > dr:
+            raise ValueError("latent_prepare: more frequencies than dr/2")
+    name = f"kvf_latent_prepare_{s}"
+    _check(
+        _fn(name, ROUTED_LIB)(
+            _ptr(x), x.stride(0), int(q_off), int(c_off), _ptr(positions), _ptr(c_weight), float(eps), _ptr(inv_freq) if rot else None, rot,
+            _ptr(slots), _ptr(cache), _ptr(qa), n, nh, dk, dr, rank, block_size, cache.shape[0] * block_size, _ptr(err), _stream(),
+        ),
+        name,
+    )  # fmt: skip
+
+
+def head_gate(y: torch.Tensor, gate: torch.Tensor, nh: int, dv: int) -> None:
+    """``y[n, h, :] *= 1 / (1 + exp(-gate[n, h]))`` in place; ``y [N, nh*dv]`` contiguous, ``gate [N, nh]``
+    a column range of a wider row."""
+    s = _suffix(y.dtype)
+    _need(y, None, "y")
+    _rows2d(gate, y.dtype, "gate")
+    n = y.shape[0]
+    if y.shape[1] != nh * dv or tuple(gate.shape) != (n, nh):
+        raise ValueError("head_gate: shapes do not agree")
+    name = f"kvf_head_gate_{s}"
+    _check(_fn(name, ROUTED_LIB)(_ptr(y), _ptr(gate), gate.stride(0), n, nh, dv, _stream()), name)
+
+
+def moe_max_tiles(n_pairs: int, num_experts: int) -> int:
+    return int(_fn("kvf_moe_max_tiles", ROUTED_LIB)(int(n_pairs), int(num_experts)))
+
+
+def moe_route(
+    x: torch.Tensor, router: torch.Tensor, correction: torch.Tensor | None, top: int, groups: int, keep: int, norm_eps: float,
+    ids: torch.Tensor, weights: torch.Tensor,
+) -> None:  # fmt: skip
+    """Per token of ``x [N, W]``: logits ``router [E, W] x`` in float, scores ``s = sigmoid(z)``; the ``top``
+    experts with the largest ``s + correction`` among the best ``keep`` of ``groups`` equal groups of
+    neighbouring experts (a group's score: the sum of its two largest ``s + correction``) are chosen
+    (``ids`` int32 ``[N, top]``); their weights are their ``s`` over the sum of those (+ ``norm_eps``)
+    (``weights`` float ``[N, top]``)."""
+    s = _suffix(x.dtype)
+    _rows2d(x, None, "x")
+    _need(router, torch.float32, "router")
+    n, w = x.shape
+    e = router.shape[0]
+    if router.dim() != 2 or router.shape[1] != w:
+        raise ValueError("moe_route: router must be [E, W]")
+    if correction is not None:
+        _need(correction, torch.float32, "correction")
+        if correction.numel() != e:
+            raise ValueError("moe_route: one correction per expert")
+    _need(ids, torch.int32, "ids")
+    _need(weights, torch.float32, "weights")
+    if tuple(ids.shape) != (n, top) or tuple(weights.shape) != (n, top):
+        raise ValueError("moe_route: ids and weights must be [N, top]")
+    name = f"kvf_moe_route_{s}"
+    _check(
+        _fn(name, ROUTED_LIB)(_ptr(x), x.stride(0), _ptr(router), _ptr(correction), n, w, e, int(top), int(groups), int(keep), float(norm_eps), _ptr(ids), _ptr(weights), _stream()),
+        name,
+    )
+
+
+def moe_experts(
+    x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, scratch: dict, resid: torch.Tensor,
+) -> None:  # fmt: skip
+    """``resid[n] += sum_k weights[n, k] * w_down[e] gelu(w_up[e] x[n])`` with ``e = ids[n, k]``: the pairs are
+    ordered by expert, every expert's rows go through its two products in tiles, and the results are
+    summed per token in the order of ``k``.  ``w_up [E, ff, W]``, ``w_down [E, W, ff]``; ``scratch``: ``order``
+    int32 ``[N*top]``, ``tiles`` int32 ``[3*max_tiles]``, ``meta`` int32 ``[4]``, ``act [N*top, ff]``, ``y`` float
+    ``[N*top, W]``.  Four launches."""
+    s = _suffix(x.dtype)
+    _rows2d(x, None, "x")
+    _need(w_up, x.dtype, "w_up")
+    _need(w_down, x.dtype, "w_down")
+    _need(resid, torch.float32, "resid")
+    n, w = x.shape
+    e, ff = w_up.shape[0], w_up.shape[1]
+    top = ids.shape[1]
+    if tuple(w_up.shape) != (e, ff, w) or tuple(w_down.shape) != (e, w, ff) or tuple(resid.shape) != (n, w):
+        raise ValueError("moe_experts: shapes do not agree")
+    _need(ids, torch.int32, "ids")
+    _need(weights, torch.float32, "weights")
+    order, tiles, meta, act, y = (scratch[k] for k in ("order", "tiles", "meta", "act", "y"))
+    _need(order, torch.int32, "order")
+    _need(tiles, torch.int32, "tiles")
+    _need(meta, torch.int32, "meta")
+    _need(act, x.dtype, "act")
+    _need(y, torch.float32, "y")
+    if order.numel() < n * top or tiles.numel() < 3 * moe_max_tiles(n * top, e) or act.numel() < n * top * ff or y.numel() < n * top * w:
+        raise ValueError("moe_experts: a scratch buffer is too small")
+    name = f"kvf_moe_experts_{s}"
+    _check(
+        _fn(name, ROUTED_LIB)(
+            _ptr(x), x.stride(0), _ptr(w_up), _ptr(w_down), _ptr(ids), _ptr(weights), n, w, ff, e, top, _ptr(order), _ptr(tiles), _ptr(meta),
+            _ptr(act), _ptr(y), _ptr(resid), _stream(),
+        ),
+        name,
+        4,
     )  # fmt: skip

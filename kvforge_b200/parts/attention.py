@@ -24,6 +24,40 @@ from .projection import PART_ROWS, project
 # the context at most) hold their places until their cluster is done.
 CLUSTER_MERGE_MAX_PAIRS = 16
 
+
+def distance_buckets(rows: int, far: int) -> torch.Tensor:
+    """Row of a distance-bias table of ``rows`` rows for every distance ``0 .. far`` (int32): the first
+    half of the rows is one distance each, ``n -> n`` for ``n < rows // 2``; the second half divides the
+    distances from ``rows // 2`` to ``far`` into steps of equal ratio,
+    ``n -> half + floor(log(n / half) / log(far / half) * (rows - half))``, at most the last row, which also
+    takes every distance beyond ``far``."""
+    half = rows // 2
+    if rows < 2 or far <= half:
+        raise ValueError("a distance-bias table needs at least two rows and a farthest distance beyond half its rows")
+    out = []
+    for n in range(far + 1):
+        out.append(n if n < half else min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half)))))
+    return torch.tensor(out, dtype=torch.int32)
+
+
+def decode_scratch(rt, ctx, nh: int, nkv: int, d: int, dv: int, tickets: torch.Tensor | None):
+    """What the decode form of attention (key ranges in parallel, then a merge) needs for this step:
+    ((partial results, their maxima and sums, tickets), the longest context the grid reaches, keys per
+    range).  Buffers are made for the longest context the engine takes; the grid follows the longest
+    context of this step (of this graph, when the step is captured)."""
+    bound = max(ctx.context_bound, ctx.max_context_len, rt.max_model_len, 1)
+    reach = max(ctx.context_bound if ctx.context_bound > 0 else ctx.max_context_len, 1)
+    # 32-bit: one range size whatever the batch, so a request's sums come in the same order beside
+    # any number of others; bfloat16: longer ranges for many sequences (fewer CTAs, same bytes)
+    split = ops.attention_split_size(ctx.num_seqs if rt.dtype == torch.bfloat16 else 1, nkv, bound, reach, d)
+    # made for the smallest range size, so that one buffer serves every batch size
+    smallest = min(ops.attention_split_size(1, 1, bound), ops.attention_split_size(ops.ATTN_SHORT_RANGE_PAIRS[0], 1, bound))
+    sa, sm = ops.attention_scratch_shapes(max(rt.max_seqs, ctx.num_seqs), nh, dv, bound, smallest)
+    acc = rt.buf("attn.part_acc", sa[0] * sa[1] * sa[2], sa[3], torch.float32, cap=0).view(sa)
+    ml = rt.buf("attn.part_ml", sm[0] * sm[1] * sm[2], sm[3], torch.float32, cap=0).view(sm)
+    return (acc, ml, tickets), reach, split
+
+
 @register_mixer("paged_attention")
 class PagedAttention(Mixer):
     """params: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``; optional
@@ -31,12 +65,18 @@ class PagedAttention(Mixer):
     sees, itself included; ``None`` = all), ``scale`` (default ``1/sqrt(head_dim)``),
     ``v_head_dim`` (size of a value head, default ``head_dim``) and ``conv`` (taps of a short causal
     convolution over time on every channel of q, k and v, between the projection and the rotation;
-    its last ``conv - 1`` inputs are the mixer's state per request; tensors ``q_proj.conv`` ...).
+    its last ``conv - 1`` inputs are the mixer's state per request; tensors ``q_proj.conv`` ...),
+    ``qk_norm`` (``{"eps": e}``: every query and key head is RMS-normed over its dims, with the tensors
+    ``q_norm.weight`` / ``k_norm.weight`` of ``head_dim`` entries shared by the heads, before any rotation),
+    ``distance_bias`` (``{"rows": B, "far": D}``: the tensor ``rel [B, num_heads]`` is added to the scaled
+    scores by ``distance_buckets`` of the distance between query and key) and ``keep_first`` (with a
+    window: the first keys of a sequence that every later query sees, at their true positions).
 
     Rotation of split pairs with equal key and value sizes and no convolution takes the kernels
-    of the Llama decoder; anything else (interleaved pairs, a value size of its own, a convolution)
-    goes through ``forward_general``: one product, the convolution, the general rotary kernel, and
-    the attention kernel that takes the shape."""
+    of the Llama decoder; anything else (interleaved pairs, a value size of its own, a convolution,
+    normed heads, a bias, kept first keys) goes through ``forward_general``: one product, the
+    convolution, the rotary kernel (or the one that also norms the heads), and the attention kernel
+    that takes the shape."""
 
     def __init__(self, params, prefix=""):
         super().__init__(params, prefix)
@@ -61,6 +101,13 @@ class PagedAttention(Mixer):
         self.taps = int(params.get("conv") or 0)
         if self.taps < 0:
             raise ValueError("conv must be a number of taps")
+        qk = params.get("qk_norm")
+        self.qk_eps = float(qk["eps"]) if qk else None
+        bias = params.get("distance_bias")
+        self.bias_shape = (int(bias["rows"]), int(bias["far"])) if bias else None
+        self.keep_first = int(params.get("keep_first") or 0)
+        if self.keep_first < 0 or (self.keep_first and self.window is None):
+            raise ValueError("keep_first is a count of keys and needs a window")
         self.q_dim = self.nh * self.d
         self.o_dim = self.nh * self.dv
         self.qkv_dim = (self.nh + self.nkv) * self.d + self.nkv * self.dv
@@ -80,13 +127,18 @@ class PagedAttention(Mixer):
             out["q_proj.conv"] = WeightDecl((nh * d, taps), kind="vector", init="conv")
             out["k_proj.conv"] = WeightDecl((nkv * d, taps), kind="vector", init="conv")
             out["v_proj.conv"] = WeightDecl((nkv * dv, taps), kind="vector", init="conv")
+        if params.get("qk_norm"):
+            out["q_norm.weight"] = WeightDecl((d,), kind="vector", init="ones")
+            out["k_norm.weight"] = WeightDecl((d,), kind="vector", init="ones")
+        if params.get("distance_bias"):
+            out["rel"] = WeightDecl((int(params["distance_bias"]["rows"]), nh), kind="vector", init="small")
         return out
 
     def cache_need(self) -> CacheNeed:
         v = None if self.dv == self.d else self.dv
         if self.window is None:
             return CacheNeed("full", self.nkv, self.d, None, v)
-        return CacheNeed("window", self.nkv, self.d, int(self.window), v)
+        return CacheNeed("window", self.nkv, self.d, int(self.window), v, keep_first=self.keep_first)
 
     def state_shape(self):
         return ((self.taps - 1) * self.qkv_dim,) if self.taps > 1 else None
@@ -102,7 +154,14 @@ class PagedAttention(Mixer):
         self.w_conv = None
         if self.taps:
             self.w_conv = torch.cat([weights["q_proj.conv"], weights["k_proj.conv"], weights["v_proj.conv"]], dim=0).contiguous()
-        if self.dv == self.d and ops.tcgen05_attention_supported(rt.dtype, self.nh, self.nkv, self.d, False):
+        self.q_norm_w = weights.get("q_norm.weight") if self.qk_eps is not None else None
+        self.k_norm_w = weights.get("k_norm.weight") if self.qk_eps is not None else None
+        self.bias = None
+        if self.bias_shape is not None:
+            self.bias = ops.DistanceBias(weights["rel"].contiguous(), distance_buckets(*self.bias_shape).to(rt.device))
+        # kept first keys and a bias on the scores are the FP32-pipe kernel's alone
+        plain_scores = self.bias is None and not self.keep_first
+        if plain_scores and self.dv == self.d and ops.tcgen05_attention_supported(rt.dtype, self.nh, self.nkv, self.d, False):
             self._query_tile = ops.tcgen05_query_tile(self.nh, self.nkv)
             rt.query_tile_sizes.add(self._query_tile)
         if self.position_spec is not None and self.position is None:
@@ -112,27 +171,18 @@ class PagedAttention(Mixer):
         # no table: q and k are stored and used as the projections leave them
         self.inv_freq = table if table is not None else torch.empty(0, dtype=torch.float32, device=rt.device)
         self.interleaved = bool(getattr(self.position, "pairs_interleaved", False))
-        self.general = bool(self.taps) or self.dv != self.d or self.interleaved
+        self.general = bool(self.taps) or self.dv != self.d or self.interleaved or self.qk_eps is not None or not plain_scores
+        if self.qk_eps is not None and table is not None and not self.interleaved:
+            raise ValueError("normed heads with a rotation of split pairs are not built (interleaved pairs are)")
 
     def _scratch(self, ctx):
         rt = self.rt
-        # buffers are made for the longest context the engine takes; the grid follows the longest
-        # context of this step (of this graph, when the step is captured)
-        bound = max(ctx.context_bound, ctx.max_context_len, rt.max_model_len, 1)
-        reach = max(ctx.context_bound if ctx.context_bound > 0 else ctx.max_context_len, 1)
-        # 32-bit: one range size whatever the batch, so a request's sums come in the same order beside
-        # any number of others; bfloat16: longer ranges for many sequences (fewer CTAs, same bytes)
-        split = ops.attention_split_size(ctx.num_seqs if rt.dtype == torch.bfloat16 else 1, self.nkv, bound, reach, self.d)
-        # made for the smallest range size, so that one buffer serves every batch size
-        smallest = min(ops.attention_split_size(1, 1, bound), ops.attention_split_size(ops.ATTN_SHORT_RANGE_PAIRS[0], 1, bound))
-        sa, sm = ops.attention_scratch_shapes(max(rt.max_seqs, ctx.num_seqs), self.nh, self.dv, bound, smallest)
-        acc = rt.buf("attn.part_acc", sa[0] * sa[1] * sa[2], sa[3], torch.float32, cap=0).view(sa)
-        ml = rt.buf("attn.part_ml", sm[0] * sm[1] * sm[2], sm[3], torch.float32, cap=0).view(sm)
-        if self._tickets.numel() < sa[0] * self.nkv:
+        seqs = max(rt.max_seqs, ctx.num_seqs)
+        if self._tickets.numel() < seqs * self.nkv:
             if rt.capturing or rt.graphs_captured:
                 raise RuntimeError("the attention tickets would have to grow after or during graph capture")
-            self._tickets = torch.zeros(sa[0] * self.nkv, dtype=torch.int32, device=rt.device)
-        return (acc, ml, self._tickets), reach, split
+            self._tickets = torch.zeros(seqs * self.nkv, dtype=torch.int32, device=rt.device)
+        return decode_scratch(rt, ctx, self.nh, self.nkv, self.d, self.dv, self._tickets)
 
     def forward(self, ctx, x: torch.Tensor, cache) -> torch.Tensor:
         rt = self.rt
@@ -184,17 +234,23 @@ class PagedAttention(Mixer):
             mixed = rt.buf("attn.qkv_conv", n, self.qkv_dim)
             ops.causal_conv(qkv, self.w_conv, cache.state, ctx.query_start_loc, ctx.state_slots, ctx.num_seqs, mixed, max_query_len=ctx.max_query_len)
             qkv = mixed
-        ops.rope_cache_general(
-            qkv, ctx.positions, self.inv_freq, self.interleaved, ctx.slot_mappings[cache.group], cache.k, cache.v,
-            self.nh, self.nkv, self.d, self.dv, ctx.block_size, rt.err,
-        )  # fmt: skip
+        if self.qk_eps is not None:
+            ops.head_norm_cache(
+                qkv, ctx.positions, self.q_norm_w, self.k_norm_w, self.qk_eps, self.inv_freq, ctx.slot_mappings[cache.group], cache.k, cache.v,
+                self.nh, self.nkv, self.d, self.dv, ctx.block_size, rt.err,
+            )  # fmt: skip
+        else:
+            ops.rope_cache_general(
+                qkv, ctx.positions, self.inv_freq, self.interleaved, ctx.slot_mappings[cache.group], cache.k, cache.v,
+                self.nh, self.nkv, self.d, self.dv, ctx.block_size, rt.err,
+            )  # fmt: skip
         out = rt.buf("attn.out", n, self.o_dim)
         self.attend(ctx, qkv, self.qkv_dim, out, cache)
         return project(rt, "attn.proj", out, self.w_o, ctx)
 
     def attend(self, ctx, q, q_stride, out, cache) -> None:
         scratch, bound, split = None, None, 256
-        common = dict(window=int(self.window or 0), q_stride=q_stride, err=self.rt.err, dv=self.dv)
+        common = dict(window=int(self.window or 0), q_stride=q_stride, err=self.rt.err, dv=self.dv, keep_first=self.keep_first, bias=self.bias)
         args = (q, out, cache.k, cache.v, ctx.block_tables[cache.group], ctx.query_start_loc, ctx.context_lens, ctx.num_seqs)
         shape = (self.nh, self.nkv, self.d, self.scale)
         # bfloat16: the decode kernel may lengthen its key ranges from the step's longest context (the merge

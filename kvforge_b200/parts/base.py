@@ -63,13 +63,16 @@ class WeightDecl:
 @dataclass(frozen=True)
 class CacheNeed:
     """What a mixer keeps per token.  ``kind``: ``full`` (every key), ``window`` (the last
-    ``window`` keys) or ``none``."""
+    ``window`` keys, and for good the first ``keep_first``) or ``none``."""
 
     kind: str
     kv_heads: int = 0
     head_dim: int = 0
     window: int | None = None
     v_head_dim: int | None = None  # size of a value head when it differs from a key head's
+    keep_first: int = 0  # window only: the first positions of a sequence that stay visible at any distance
+    # the value of a token is the first ``v_head_dim`` numbers of its key (a shared latent): one tensor holds both
+    v_in_k: bool = False
 
     @property
     def value_dim(self) -> int:
@@ -77,7 +80,7 @@ class CacheNeed:
 
     @property
     def group_key(self) -> tuple:
-        return (self.kind, self.kv_heads, self.head_dim, self.window, self.value_dim)
+        return (self.kind, self.kv_heads, self.head_dim, self.window, self.value_dim, self.keep_first, self.v_in_k)
 
 
 @dataclass
@@ -94,7 +97,7 @@ class LayerCache:
     """The pages one mixer call reads and, if ``writable``, writes."""
 
     k: torch.Tensor  # [num_blocks, kv_heads, block_size, head_dim]
-    v: torch.Tensor  # [num_blocks, kv_heads, block_size, value head_dim]
+    v: torch.Tensor  # [num_blocks, kv_heads, block_size, value head_dim]; ``k`` itself where values lie inside the keys
     group: int  # index of the cache group: selects the block table and slots in the context
     writable: bool = True
     state: torch.Tensor | None = None  # [num_slots, *state_shape] if the mixer has state

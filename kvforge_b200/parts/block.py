@@ -55,6 +55,50 @@ class PreNormBlock(Block):
         return self.ffn.forward(ctx, x)
 
 
+@register_block("parallel")
+class ParallelBlock(Block):
+    """One norm a layer; the mixer and the feed-forward both read its output and both add to the
+    stream: ``h = h + mixer(n(h)) + ffn(n(h))``.  params: ``norm``, ``mixer``, ``ffn`` (``PartSpec``
+    each; ``ffn`` may be ``None``: a layer without a feed-forward) and the stems ``norm_name``,
+    ``mixer_name``, ``ffn_name`` under the layer's prefix.
+
+    Nothing reads the residual stream between the norm and the next layer's norm, so either part may
+    add its result straight into the stream (``ops.ADDED``); of two results that are still pending
+    one is added here and the other is handed to the next norm."""
+
+    def __init__(self, params, prefix=""):
+        super().__init__(params, prefix)
+        self.norm = build_part("norm", _spec(params["norm"]), _stem(prefix, params.get("norm_name", "norm1")))
+        self.mixer = build_part("mixer", _spec(params["mixer"]), _stem(prefix, params.get("mixer_name", "mix")))
+        self.ffn = None
+        if params.get("ffn") is not None:
+            self.ffn = build_part("ffn", _spec(params["ffn"]), _stem(prefix, params.get("ffn_name", "mlp")))
+
+    def sub_parts(self):
+        return [p for p in (self.norm, self.mixer, self.ffn) if p is not None]
+
+    def mixer_part(self):
+        return self.mixer
+
+    def forward(self, ctx, resid, delta, cache):
+        x = self.norm.forward(ctx, resid, delta)
+        a = self.mixer.forward(ctx, x, cache)
+        if self.ffn is None:
+            return a
+        f = self.ffn.forward(ctx, x)
+        if a is ops.ADDED or a is None:
+            return f
+        if f is ops.ADDED or f is None:
+            return a
+        n = resid.shape[0]
+        if isinstance(f, ops.Partials):
+            for s in range(f.nsplit):
+                ops.add_residual(resid, f.t[s, :n])
+        else:
+            ops.add_residual(resid, f[:n])
+        return a
+
+
 @register_block("stream_prenorm")
 class StreamPreNormBlock(Block):
     """The pre-norm arrangement over several residual streams (hyper-connections).  A token has

@@ -10,13 +10,15 @@ from .base import Embedding, WeightDecl, register_embedding
 
 @register_embedding("token_embedding")
 class TokenEmbedding(Embedding):
-    """params: ``vocab_size``, ``hidden_size``.  A token id outside the table raises the device
+    """params: ``vocab_size``, ``hidden_size``; optional ``scale`` (every row is multiplied by it, in
+    32-bit, as it enters the residual stream).  A token id outside the table raises the device
     error flag (bit 0) and reads row 0."""
 
     def __init__(self, params, prefix=""):
         super().__init__(params, prefix)
         self.vocab = int(params["vocab_size"])
         self.hidden = int(params["hidden_size"])
+        self.scale = float(params.get("scale") or 1.0)
 
     @classmethod
     def weight_decls(cls, params):
@@ -30,4 +32,4 @@ class TokenEmbedding(Embedding):
         return self.weight
 
     def forward(self, ctx, resid):
-        ops.embed(self.weight, ctx.token_ids, resid, self.rt.err, ctx.feedback_rows, ctx.token_feedback)
+        ops.embed(self.weight, ctx.token_ids, resid, self.rt.err, ctx.feedback_rows, ctx.token_feedback, self.scale)

@@ -1,0 +1,84 @@
+"""A feed-forward of many small experts of which every token uses a few.
+
+Expert ``e`` is ``W_down[e] act(W_up[e] x)`` without biases.  The router's logits ``z = W_router x``
+and everything made of them are 32-bit: scores ``s = sigmoid(z)``; the choice is made on
+``s + correction`` (a tensor that shifts the choice, not the weights), among the experts of the best
+groups only when the experts form groups; the chosen experts' results are summed with weights
+``s / (sum of the chosen s + 1e-20)``.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from .base import FeedForward, WeightDecl, register_feed_forward
+
+WEIGHT_SUM_EPS = 1e-20  # added to the sum of the chosen scores before the division
+
+
+@register_feed_forward("routed_experts")
+class RoutedExperts(FeedForward):
+    """params: ``hidden_size``, ``experts``, ``top``, ``intermediate_size`` (of one expert), ``activation``
+    (only ``"gelu"``, the exact one); optional ``groups`` and ``keep`` (the experts form ``groups`` equal
+    groups of neighbours; a group's score is the sum of its two largest choice scores and only experts
+    of the best ``keep`` groups can be chosen) and ``correction`` (default true: the tensor
+    ``correction [experts]`` is added to the scores for the choice).
+
+    Tensors: ``router [E, W]``, ``correction [E]``, ``e<i>.up [ff, W]``, ``e<i>.down [W, ff]``."""
+
+    def __init__(self, params, prefix=""):
+        super().__init__(params, prefix)
+        p = params
+        self.hidden, self.experts, self.top, self.ff = int(p["hidden_size"]), int(p["experts"]), int(p["top"]), int(p["intermediate_size"])
+        self.groups = int(p.get("groups") or 1)
+        self.keep = int(p.get("keep") or self.groups)
+        self.corrected = bool(p.get("correction", True))
+        if p.get("activation", "gelu") != "gelu":
+            raise ValueError("the experts' activation is 'gelu'")
+        if not 0 < self.top <= self.experts or self.experts % self.groups or not 0 < self.keep <= self.groups:
+            raise ValueError("experts must divide into the groups, and top and keep must be within their counts")
+        if self.top > self.keep * (self.experts // self.groups):
+            raise ValueError("the groups that stay hold fewer experts than a token uses")
+
+    @classmethod
+    def weight_decls(cls, params):
+        w, e, ff = int(params["hidden_size"]), int(params["experts"]), int(params["intermediate_size"])
+        out = {"router": WeightDecl((e, w), kind="vector", init="normal")}
+        if params.get("correction", True):
+            out["correction"] = WeightDecl((e,), kind="vector", init="zeros")
+        for i in range(e):
+            out[f"e{i}.up"] = WeightDecl((ff, w))
+            out[f"e{i}.down"] = WeightDecl((w, ff))
+        return out
+
+    def bind(self, weights, rt):
+        super().bind(weights, rt)
+        self.router = weights["router"].contiguous()
+        self.correction = weights["correction"].contiguous() if self.corrected else None
+        self.w_up = torch.stack([weights[f"e{i}.up"] for i in range(self.experts)]).contiguous()
+        self.w_down = torch.stack([weights[f"e{i}.down"] for i in range(self.experts)]).contiguous()
+        self._meta = torch.zeros(4, dtype=torch.int32, device=rt.device)
+
+    def forward(self, ctx, x: torch.Tensor):
+        rt = self.rt
+        n, top, e = x.shape[0], self.top, self.experts
+        pairs_cap = rt.max_tokens * top
+        ids = rt.buf("experts.ids", n, top, torch.int32)
+        wts = rt.buf("experts.weights", n, top, torch.float32)
+        ops.moe_route(x, self.router, self.correction, top, self.groups, self.keep, WEIGHT_SUM_EPS, ids, wts)
+        scratch = {
+            "order": rt.buf("experts.order", n * top, 1, torch.int32, cap=pairs_cap),
+            "tiles": rt.buf("experts.tiles", ops.moe_max_tiles(n * top, e), 3, torch.int32, cap=ops.moe_max_tiles(pairs_cap, e)),
+            "meta": self._meta,
+            "act": rt.buf("experts.act", n * top, self.ff, cap=pairs_cap),
+            "y": rt.buf("experts.y", n * top, self.hidden, torch.float32, cap=pairs_cap),
+        }
+        resid = getattr(ctx, "residual", None)
+        if resid is not None and resid.shape[0] >= n and resid.shape[1] == self.hidden:
+            ops.moe_experts(x, self.w_up, self.w_down, ids, wts, scratch, resid[:n])
+            return ops.ADDED
+        out = rt.buf("experts.out", n, self.hidden, torch.float32)
+        out.zero_()
+        ops.moe_experts(x, self.w_up, self.w_down, ids, wts, scratch, out)
+        return ops.Partials(out.view(1, n, self.hidden))

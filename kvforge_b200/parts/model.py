@@ -30,6 +30,9 @@ class LayerSpec:
 class LayerCall:
     layer: int
     kv_from: int | None = None  # index (in the execution list) of the call whose cache is read
+    # row of the model's ``pass_offsets`` tensor that is added to every token of the residual stream right
+    # before this call (a stretch of layers that runs several times marks each pass so)
+    offset_row: int | None = None
 
 
 @dataclass
@@ -61,6 +64,9 @@ class ModelSpec:
     # how many residual streams a token has (hyper-connections); the blocks' arrangement reads and writes
     # them, all start as the embedding's output, and the final norm reads their sum
     residual_streams: int = 1
+    # float tensor ``[rows, hidden]`` whose rows the calls' ``offset_row`` name, and its checkpoint name
+    pass_offsets: int = 0
+    pass_offsets_name: str = "loop.step"
 
     def __post_init__(self) -> None:
         if not self.execution:
@@ -68,6 +74,8 @@ class ModelSpec:
         for idx, call in enumerate(self.execution):
             if not 0 <= call.layer < len(self.layers):
                 raise ValueError(f"execution[{idx}] names layer {call.layer}, which does not exist")
+            if call.offset_row is not None and not 0 <= call.offset_row < self.pass_offsets:
+                raise ValueError(f"execution[{idx}].offset_row names a row that pass_offsets does not have")
             if call.kv_from is not None:
                 if not 0 <= call.kv_from < idx:
                     raise ValueError(f"execution[{idx}].kv_from must name an earlier call")
@@ -141,6 +149,8 @@ class DecoderModel:
         for part in self._all_parts():
             for local, decl in type(part).weight_decls(part.params).items():
                 out[part.tensor_name(local)] = decl
+        if self.spec.pass_offsets:
+            out[self.spec.pass_offsets_name] = WeightDecl((self.spec.pass_offsets, self.spec.hidden_size), kind="vector", init="zeros")
         return out
 
     def _all_parts(self):
@@ -177,6 +187,9 @@ class DecoderModel:
             part.bind(local, rt)
         # kvforge: one tensor when tied, and the embedding stands in when the head is absent
         # (src/tokenvault/model.py:157-158, src/tokenvault/model_loader.py:105-106)
+        self.pass_offsets = weights[s.pass_offsets_name] if s.pass_offsets else None
+        if s.pass_offsets and s.residual_streams != 1:
+            raise ValueError("rows added between passes need a single residual stream")
         if s.tie_word_embeddings or self.head.tensor_name("weight") not in weights:
             self.head.tie(self.embedding.table())
 
@@ -202,6 +215,10 @@ class DecoderModel:
             resid, ctx.residual = streams, None
         delta = None
         for idx, call in enumerate(self.spec.execution):
+            if call.offset_row is not None:
+                # the sum still pending from the layer before is added by this layer's norm: the order of the two
+                # additions does not matter beyond rounding
+                ops.add_row(resid, self.pass_offsets[call.offset_row])
             delta = self.blocks[call.layer].forward(ctx, resid, delta, self.caches[idx])
         return resid, delta
 

@@ -15,20 +15,22 @@ from .base import Norm, WeightDecl, register_norm
 
 @register_norm("rmsnorm")
 class RMSNorm(Norm):
-    """params: ``dim``, ``eps``."""
+    """params: ``dim``, ``eps``; optional ``one_plus`` (the tensor is stored around zero and the rows
+    are multiplied by ``1 + w``; the sum is made once, in 32-bit, when the tensor is bound)."""
 
     def __init__(self, params, prefix=""):
         super().__init__(params, prefix)
         self.dim = int(params["dim"])
         self.eps = float(params["eps"])
+        self.one_plus = bool(params.get("one_plus", False))
 
     @classmethod
     def weight_decls(cls, params):
-        return {"weight": WeightDecl((int(params["dim"]),), kind="vector", init="ones")}
+        return {"weight": WeightDecl((int(params["dim"]),), kind="vector", init="zeros" if params.get("one_plus") else "ones")}
 
     def bind(self, weights, rt):
         super().bind(weights, rt)
-        self.weight = weights["weight"]
+        self.weight = weights["weight"] + 1.0 if self.one_plus else weights["weight"]
 
     def forward(self, ctx, resid: torch.Tensor, delta, rows: torch.Tensor | None = None, num_rows: int | None = None):
         """``delta``: ``None``, a tensor in the storage type, or ``ops.Partials``."""
