@@ -600,13 +600,14 @@ def run_load(cfg, nreq: int, short_prompts: bool = False) -> dict:
             "tpot_p50_ms": round(m["tpot_p50_ms"], 3), "preemptions": stats["scheduler"]["num_preemptions"]}  # fmt: skip
 
 
-DESIGN_PAIRS = (("mopilorn-1b", "llama-3.2-1b"), ("mopilorn-3b", "llama-3.2-3b"))
+DESIGN_PAIRS = (("mopilorn-1b", "llama-3.2-1b"), ("mopilorn-3b", "llama-3.2-3b"), ("setenex-1b", "llama-3.2-1b"))
 
 
 def run_designs(args) -> dict:
-    """Prompt and decode throughput of the Mopilorn shapes beside the Llama shapes of equal width, depth,
-    feed-forward and vocabulary (random weights): a prompt of 2,048 tokens, and decode steps of 8 and 64 requests
-    with 2,048 tokens behind them, each as captured graphs, timed on the device."""
+    """Prompt and decode throughput of the Mopilorn and Setenex shapes beside the Llama shapes of equal width,
+    depth, feed-forward per token and vocabulary (random weights): a prompt of 2,048 tokens, and decode steps of 8
+    and 64 requests with 2,048 tokens behind them, each as captured graphs, timed on the device.  ``--design NAME``
+    runs the one pair that holds the named shape."""
     import gc
 
     import torch
@@ -615,8 +616,14 @@ def run_designs(args) -> dict:
 
     out = {"only": "designs", "prompt_tokens": PREFILL_TOKENS, "decode_context": PROMPT_LEN, "shapes": {}}
     steps, warmup = max(8, min(args.steps, 64)), max(3, args.warmup)
+    done = set()
     for pair in DESIGN_PAIRS:
+        if args.design and args.design not in pair:
+            continue
         for name in pair:
+            if name in done:
+                continue
+            done.add(name)
             cfg = PRESETS[name]
             row = {}
             core = make_core(cfg, 64, PREFILL_TOKENS, PROMPT_LEN + steps + warmup + 32)
@@ -848,7 +855,8 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", choices=["own", "reference"], default="own")
-    ap.add_argument("--only", choices=["decode", "prefill", "mixed", "attention", "attention-prefill", "gemm", "sample", "load", "designs"], help="run one part alone and print a short line (for profiling); 'designs': the Mopilorn shapes beside the Llama shapes of equal size")
+    ap.add_argument("--only", choices=["decode", "prefill", "mixed", "attention", "attention-prefill", "gemm", "sample", "load", "designs"], help="run one part alone and print a short line (for profiling); 'designs': the Mopilorn and Setenex shapes beside the Llama shapes of equal size")
+    ap.add_argument("--design", default=None, help="with --only designs: the one pair that holds this named shape (default: all pairs)")
     ap.add_argument("--preset", default="llama-3.2-1b", help="with --only: the shape (llama-3.2-1b, llama-3.2-3b, llama-3.1-8b, mopilorn-1b, mopilorn-3b)")
     ap.add_argument("--split", type=int, default=0, help="with --only attention: keys per range (0 = the engine's choice)")
     ap.add_argument("--block-size", type=int, default=16, help="with --only attention / attention-prefill: tokens per page")

@@ -6,9 +6,9 @@
 //   product : for every tile of one expert's rows a tile of  act(x W_up^T)  or of  h W_down^T
 //   combine : resid[token] += sum_k weight_k * y[token, k]   (float, k in order)
 //
-// A pair's row of a product depends on that row and on its expert's weights alone (one thread adds
-// its products in the order of k), so a token's result does not depend on what else is in the batch
-// or on where its pairs land in the order.  Router, scores, choice and the weighted sum are float
+// A pair's row of a product depends on that row and on its expert's weights alone (its products are
+// added in the order of k: by one thread on the FP32 pipes, by the tensor cores' own order in bfloat16),
+// so a token's result does not depend on what else is in the batch or on where its pairs land in the order.  Router, scores, choice and the weighted sum are float
 // whatever the storage type T.
 #include <limits.h>
 
@@ -18,7 +18,8 @@ using namespace kvf;
 
 namespace {
 
-constexpr int TM = 32;  // rows of a tile of the grouped products
+constexpr int TM = 32;  // rows of a tile of the grouped products on the FP32 pipes
+constexpr int TM_MIN = 8;  // the smallest tile any product uses: scratch for the tile list is made for it
 
 __device__ __forceinline__ void warp_argmax(float& v, int& i) {
 #pragma unroll
@@ -126,8 +127,8 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const T* __restrict__ x,
 }
 
 // One CTA.  ids [P] -> order [P] (pairs by expert), tiles: (expert, first sorted row, rows) per tile of
-// TM rows, meta[0] = number of tiles.
-__global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ ids, int P, int E, int* __restrict__ order,
+// tm rows, meta[0] = number of tiles.
+__global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ ids, int P, int E, int tm, int* __restrict__ order,
                                                          int* __restrict__ tiles, int* __restrict__ meta) {
   pdl_launch();
   pdl_wait();
@@ -145,17 +146,17 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ 
       off[e] = run;
       tbase[e] = t;
       run += cnt[e];
-      t += (cnt[e] + TM - 1) / TM;
+      t += (cnt[e] + tm - 1) / tm;
     }
     meta[0] = t;
   }
   __syncthreads();
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
     const int c = cnt[e];
-    for (int r0 = 0, t = tbase[e]; r0 < c; r0 += TM, ++t) {
+    for (int r0 = 0, t = tbase[e]; r0 < c; r0 += tm, ++t) {
       tiles[3 * t] = e;
       tiles[3 * t + 1] = off[e] + r0;
-      tiles[3 * t + 2] = min(TM, c - r0);
+      tiles[3 * t + 2] = min(tm, c - r0);
     }
   }
   __syncthreads();
@@ -238,6 +239,173 @@ __global__ void __launch_bounds__(256) moe_product_kernel(const T* __restrict__ 
   }
 }
 
+// ---------------------------------------------------------------- the same products on the tensor cores (bfloat16)
+// A tile of up to NT * 8 rows of one expert times 64 of its output columns over the whole of K: the expert's
+// weights ride the MMA's 16-row side (mma.sync m16n8k16) and the tile's rows its 8-column side, as in the
+// decode product of the dense layers; weights and gathered rows come in through a cp.async pipeline of
+// 16-byte chunks in XOR-swizzled rows.  With a few rows an expert (decoding) the kernel streams each chosen
+// expert's weights once; with many it reads them once per tile of rows, from L2.
+__device__ __forceinline__ uint32_t s_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cpa16(uint32_t dst, const void* src, bool valid) {
+  const int sz = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(sz));
+}
+__device__ __forceinline__ void cpa_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cpa_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// 16-byte chunk `chunk` (0..7) of row `row` in a swizzled tile of 128-byte rows
+__device__ __forceinline__ uint32_t toff(int row, int chunk) { return (uint32_t)(row * 128 + ((chunk ^ (row & 7)) << 4)); }
+
+template <int NT, int STAGES, bool UP>
+__global__ void __launch_bounds__(128) moe_product_mma_kernel(const bf16* __restrict__ a, long long a_stride, const bf16* __restrict__ w,
+                                                               const int* __restrict__ order, const int* __restrict__ tiles,
+                                                               const int* __restrict__ meta, int top, int K, int n_out,
+                                                               bf16* __restrict__ act, float* __restrict__ y) {
+  constexpr int BN = 64, BK = 64, THREADS = 128;
+  constexpr int W_BYTES = BN * 128, X_ROWS = NT * 8, X_BYTES = X_ROWS * 128, STAGE_BYTES = W_BYTES + X_BYTES;
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  __shared__ int src[X_ROWS], dst[X_ROWS];
+  pdl_launch();
+  pdl_wait();
+  if ((int)blockIdx.y >= meta[0]) return;
+  const uint32_t smem = s_u32(smem_raw);
+  const int e = tiles[3 * blockIdx.y], row0 = tiles[3 * blockIdx.y + 1], rows = tiles[3 * blockIdx.y + 2];
+  const int n0 = blockIdx.x * BN;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x < X_ROWS) {
+    int s = -1, d = -1;
+    if ((int)threadIdx.x < rows) {
+      const int pair = order[row0 + threadIdx.x];
+      s = UP ? pair / top : row0 + (int)threadIdx.x;
+      d = UP ? row0 + (int)threadIdx.x : pair;
+    }
+    src[threadIdx.x] = s;
+    dst[threadIdx.x] = d;
+  }
+  __syncthreads();
+  const bf16* wb = w + (size_t)e * n_out * K;
+  const int n_iters = (K + BK - 1) / BK;
+  auto load = [&](int stage, int it) {
+    const int k0 = it * BK;
+    const uint32_t ws = smem + stage * STAGE_BYTES, xs = ws + W_BYTES;
+#pragma unroll
+    for (int i = 0; i < (BN * 8) / THREADS; ++i) {
+      const int idx = threadIdx.x + i * THREADS;
+      const int row = idx >> 3, c = idx & 7;
+      const int k = k0 + c * 8;
+      const bool valid = (n0 + row < n_out) && (k < K);
+      cpa16(ws + toff(row, c), wb + (valid ? (size_t)(n0 + row) * K + k : 0), valid);
+    }
+    for (int idx = threadIdx.x; idx < X_ROWS * 8; idx += THREADS) {
+      const int row = idx >> 3, c = idx & 7;
+      const int k = k0 + c * 8;
+      const bool valid = (src[row] >= 0) && (k < K);
+      cpa16(xs + toff(row, c), a + (valid ? (size_t)src[row] * a_stride + k : 0), valid);
+    }
+  };
+  float acc[NT][4];
+#pragma unroll
+  for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) {
+    if (s < n_iters) load(s, s);
+    cpa_commit();
+  }
+  for (int it = 0; it < n_iters; ++it) {
+    cpa_wait<STAGES - 2>();
+    __syncthreads();  // stage `it` has landed for every thread; stage `it-1` has been consumed
+    if (it + STAGES - 1 < n_iters) load((it + STAGES - 1) % STAGES, it + STAGES - 1);
+    cpa_commit();
+    const uint32_t ws = smem + (it % STAGES) * STAGE_BYTES, xs = ws + W_BYTES;
+#pragma unroll
+    for (int kk = 0; kk < BK / 16; ++kk) {
+      uint32_t af[4];
+      ldsm_x4(af, ws + toff(warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3), 2 * kk + (lane >> 4)));
+#pragma unroll
+      for (int j = 0; j < NT; j += 2) {
+        uint32_t b[4];
+        const int trow = (NT == 1) ? (lane & 7) : (j * 8 + ((lane >> 4) << 3) + (lane & 7));
+        ldsm_x4(b, xs + toff(trow, 2 * kk + ((lane >> 3) & 1)));
+        mma16816(acc[j], af, b[0], b[1]);
+        if (NT > 1) mma16816(acc[j + 1 < NT ? j + 1 : j], af, b[2], b[3]);
+      }
+    }
+  }
+  cpa_wait<0>();
+  // acc[j]: c0,c1 -> column f0 = warp*16 + lane/4, rows t, t+1; c2,c3 -> column f0 + 8
+  const int f0 = n0 + warp * 16 + (lane >> 2);
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int t = j * 8 + ((lane & 3) << 1) + r;
+      if (t >= rows) continue;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int f = f0 + 8 * h;
+        if (f >= n_out) continue;
+        const float v = acc[j][2 * h + r];
+        if (UP)
+          act[(size_t)dst[t] * n_out + f] = __float2bfloat16_rn(gelu_erf(v));
+        else
+          y[(size_t)dst[t] * n_out + f] = v;
+      }
+    }
+  }
+}
+
+template <int NT, int STAGES, bool UP>
+int launch_mma(const bf16* a, long long a_stride, const bf16* w, const int* order, const int* tiles, const int* meta, int top, int K,
+               int n_out, int max_tiles, bf16* act, float* y, cudaStream_t st) {
+  const size_t smem = (size_t)STAGES * (64 * 128 + NT * 8 * 128);
+  auto kern = moe_product_mma_kernel<NT, STAGES, UP>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return launch(kern, dim3((n_out + 63) / 64, max_tiles), dim3(128), smem, st, a, a_stride, w, order, tiles, meta, top, K, n_out, act, y);
+}
+
+template <bool UP>
+int product_mma(int tm, const bf16* a, long long a_stride, const bf16* w, const int* order, const int* tiles, const int* meta, int top, int K,
+                int n_out, int max_tiles, bf16* act, float* y, cudaStream_t st) {
+  if (tm <= 8) return launch_mma<1, 8, UP>(a, a_stride, w, order, tiles, meta, top, K, n_out, max_tiles, act, y, st);
+  if (tm <= 16) return launch_mma<2, 8, UP>(a, a_stride, w, order, tiles, meta, top, K, n_out, max_tiles, act, y, st);
+  if (tm <= 32) return launch_mma<4, 6, UP>(a, a_stride, w, order, tiles, meta, top, K, n_out, max_tiles, act, y, st);
+  return launch_mma<8, 6, UP>(a, a_stride, w, order, tiles, meta, top, K, n_out, max_tiles, act, y, st);
+}
+
+// Rows of a tile for P pairs over E experts on the tensor cores: small tiles while an expert has a few rows (the
+// weights stream once either way), large ones when it has many (its weights are read once per tile).
+inline int mma_tile_rows(int P, int E) {
+  if (P <= 2 * E) return 8;
+  if (P <= 6 * E) return 16;
+  if (P <= 24 * E) return 32;
+  return 64;
+}
+
+// xs[i, :] = x[order[i] / top, :]: the rows of the pairs in the order of the experts (16-byte copies), for a
+// product that wants an expert's rows side by side.
+__global__ void moe_gather_kernel(const bf16* __restrict__ x, long long x_stride, const int* __restrict__ order, int top, int P,
+                                  int W, bf16* __restrict__ xs) {
+  pdl_launch();
+  pdl_wait();
+  const int chunks = W / 8;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < (long long)P * chunks; idx += (long long)gridDim.x * blockDim.x) {
+    const int i = (int)(idx / chunks), c = (int)(idx - (long long)i * chunks);
+    const uint4 v = *reinterpret_cast<const uint4*>(x + (size_t)(order[i] / top) * x_stride + c * 8);
+    *reinterpret_cast<uint4*>(xs + (size_t)i * W + c * 8) = v;
+  }
+}
+
 __global__ void moe_combine_kernel(float* __restrict__ resid, const float* __restrict__ y, const float* __restrict__ wts,
                                    long long total, int W, int top) {
   pdl_launch();
@@ -253,8 +421,45 @@ __global__ void moe_combine_kernel(float* __restrict__ resid, const float* __res
 
 }  // namespace
 
-// Rows of tiles that `n_pairs` pairs spread over `E` experts can make at most.
-KVF_API int kvf_moe_max_tiles(int n_pairs, int E) { return n_pairs / TM + E; }
+// Rows of tiles that `n_pairs` pairs spread over `E` experts can make at most, whatever the tile size.
+KVF_API int kvf_moe_max_tiles(int n_pairs, int E) { return n_pairs / TM_MIN + E; }
+
+template <typename T>
+int run_products(const T* x, long long x_stride, const T* w_up, const T* w_down, const int* ids, int P, int W, int ff, int E, int top,
+                 int* order, int* tiles, int* meta, T* act, float* y, cudaStream_t st);
+
+template <>
+int run_products<float>(const float* x, long long x_stride, const float* w_up, const float* w_down, const int* ids, int P, int W, int ff,
+                        int E, int top, int* order, int* tiles, int* meta, float* act, float* y, cudaStream_t st) {
+  int rc = launch(moe_sort_kernel, dim3(1), dim3(1024), (size_t)3 * E * sizeof(int), st, ids, P, E, TM, order, tiles, meta);
+  if (rc) return rc;
+  const int max_tiles = P / TM + E;
+  rc = launch(moe_product_kernel<float, true>, dim3((ff + 63) / 64, max_tiles), dim3(256), 0, st, x, x_stride, w_up, (const int*)order,
+              (const int*)tiles, (const int*)meta, top, W, ff, act, (float*)nullptr);
+  if (rc) return rc;
+  return launch(moe_product_kernel<float, false>, dim3((W + 63) / 64, max_tiles), dim3(256), 0, st, (const float*)act, (long long)ff,
+                w_down, (const int*)order, (const int*)tiles, (const int*)meta, top, ff, W, (float*)nullptr, y);
+}
+
+template <>
+int run_products<bf16>(const bf16* x, long long x_stride, const bf16* w_up, const bf16* w_down, const int* ids, int P, int W, int ff, int E,
+                       int top, int* order, int* tiles, int* meta, bf16* act, float* y, cudaStream_t st) {
+  const bool tensor = (W % 8 == 0) && (ff % 8 == 0) && (x_stride % 8 == 0) && ((((uintptr_t)x) & 15) == 0);
+  const int tm = tensor ? mma_tile_rows(P, E) : TM;
+  int rc = launch(moe_sort_kernel, dim3(1), dim3(1024), (size_t)3 * E * sizeof(int), st, ids, P, E, tm, order, tiles, meta);
+  if (rc) return rc;
+  const int max_tiles = P / tm + E;
+  if (tensor) {
+    rc = product_mma<true>(tm, x, x_stride, w_up, order, tiles, meta, top, W, ff, max_tiles, act, nullptr, st);
+    if (rc) return rc;
+    return product_mma<false>(tm, act, (long long)ff, w_down, order, tiles, meta, top, ff, W, max_tiles, nullptr, y, st);
+  }
+  rc = launch(moe_product_kernel<bf16, true>, dim3((ff + 63) / 64, max_tiles), dim3(256), 0, st, x, x_stride, w_up, (const int*)order,
+              (const int*)tiles, (const int*)meta, top, W, ff, act, (float*)nullptr);
+  if (rc) return rc;
+  return launch(moe_product_kernel<bf16, false>, dim3((W + 63) / 64, max_tiles), dim3(256), 0, st, (const bf16*)act, (long long)ff,
+                w_down, (const int*)order, (const int*)tiles, (const int*)meta, top, ff, W, (bf16*)nullptr, y);
+}
 
 #define KVF_EXPERTS_API(SUF, T)                                                                                       \
   KVF_API int kvf_moe_route_##SUF(const void* x, long long x_stride, const float* router, const float* correction,    \
@@ -276,18 +481,9 @@ KVF_API int kvf_moe_max_tiles(int n_pairs, int E) { return n_pairs / TM + E; }
     if (n_tokens <= 0) return 0;                                                                                      \
     const int P = n_tokens * top;                                                                                     \
     if ((size_t)3 * E * sizeof(int) > 48 * 1024) return (int)cudaErrorInvalidValue;                                   \
-    int rc = launch(moe_sort_kernel, dim3(1), dim3(1024), (size_t)3 * E * sizeof(int), st, ids, P, E, order, tiles,   \
-                    meta);                                                                                            \
-    if (rc) return rc;                                                                                                \
-    const int max_tiles = kvf_moe_max_tiles(P, E);                                                                    \
-    if (max_tiles > 65535) return (int)cudaErrorInvalidValue;                                                         \
-    rc = launch(moe_product_kernel<T, true>, dim3((ff + 63) / 64, max_tiles), dim3(256), 0, st, (const T*)x,          \
-                x_stride, (const T*)w_up, (const int*)order, (const int*)tiles, (const int*)meta, top, W, ff, (T*)act, \
-                (float*)nullptr);                                                                                     \
-    if (rc) return rc;                                                                                                \
-    rc = launch(moe_product_kernel<T, false>, dim3((W + 63) / 64, max_tiles), dim3(256), 0, st, (const T*)act,        \
-                (long long)ff, (const T*)w_down, (const int*)order, (const int*)tiles, (const int*)meta, top, ff, W,   \
-                (T*)nullptr, y);                                                                                      \
+    if (kvf_moe_max_tiles(P, E) > 65535) return (int)cudaErrorInvalidValue;                                           \
+    int rc = run_products<T>((const T*)x, x_stride, (const T*)w_up, (const T*)w_down, ids, P, W, ff, E, top, order,   \
+                             tiles, meta, (T*)act, y, st);                                                            \
     if (rc) return rc;                                                                                                \
     const long long total = (long long)n_tokens * W;                                                                  \
     long long g = (total + 255) / 256;                                                                                \
@@ -298,3 +494,27 @@ KVF_API int kvf_moe_max_tiles(int n_pairs, int E) { return n_pairs / TM + E; }
 
 KVF_EXPERTS_API(f32, float)
 KVF_EXPERTS_API(bf16, bf16)
+
+// The steps one by one, for a caller that runs the two products elsewhere (the tensor-memory product of many rows).
+KVF_API int kvf_moe_sort(const int* ids, int P, int E, int tm, int* order, int* tiles, int* meta, cudaStream_t st) {
+  if (P <= 0) return 0;
+  if (tm <= 0 || (size_t)3 * E * sizeof(int) > 48 * 1024) return (int)cudaErrorInvalidValue;
+  return launch(moe_sort_kernel, dim3(1), dim3(1024), (size_t)3 * E * sizeof(int), st, ids, P, E, tm, order, tiles, meta);
+}
+
+KVF_API int kvf_moe_gather_bf16(const void* x, long long x_stride, const int* order, int top, int P, int W, void* xs,
+                                cudaStream_t st) {
+  if (P <= 0) return 0;
+  if ((W & 7) || (x_stride & 7) || ((((uintptr_t)x) | ((uintptr_t)xs)) & 15)) return (int)cudaErrorInvalidValue;
+  long long g = ((long long)P * (W / 8) + 255) / 256;
+  if (g > 148 * 16) g = 148 * 16;
+  return launch(moe_gather_kernel, dim3((unsigned)g), dim3(256), 0, st, (const bf16*)x, x_stride, order, top, P, W, (bf16*)xs);
+}
+
+KVF_API int kvf_moe_combine(float* resid, const float* y, const float* wts, int n_tokens, int W, int top, cudaStream_t st) {
+  const long long total = (long long)n_tokens * W;
+  if (total <= 0) return 0;
+  long long g = (total + 255) / 256;
+  if (g > 148 * 16) g = 148 * 16;
+  return launch(moe_combine_kernel, dim3((unsigned)g), dim3(256), 0, st, resid, y, wts, total, W, top);
+}

@@ -21,6 +21,12 @@
 // any K that is a multiple of 8 work; stores are guarded.  Every wait on an mbarrier is
 // bounded: if one runs out, the kernel raises bit 4 of the error flag and winds down (tensor
 // memory is freed) instead of hanging.  No cluster launch and no multicast.
+//
+// The grouped form (a feed-forward of routed experts) runs the same kernel over a list of row tiles
+// made on the device: rows of x are ordered by expert, tile i is (expert, first row, rows) with at most
+// 128 rows of one expert, and W holds the experts' matrices one after the other ([E * N, K]); a tile's
+// rows past its count belong to the next expert and are computed but not stored.  Its epilogues: the
+// exact GELU to bfloat16 rows in the same order, or float rows scattered by a list of row numbers.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -38,8 +44,14 @@ struct TcParams {
   void* out;
   int M, N, K;
   int ldo;
-  int mode;  // 0: bfloat16 y; 3: bfloat16 silu(g)*u
+  int mode;  // 0: bfloat16 y; 3: bfloat16 silu(g)*u; 4: bfloat16 gelu(y); 5: float y to the rows that `scatter` names
   int* err;
+  // grouped form: `tiles` holds (expert, first row, rows) per row tile, meta[0] their number (at most max_row_tiles);
+  // N is then the number of output columns of ONE expert
+  const int* tiles;
+  const int* meta;
+  const int* scatter;
+  int max_row_tiles;
 };
 
 __device__ __forceinline__ uint32_t sm_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -156,8 +168,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 
   pdl_launch();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m_tiles = (p.M + BM - 1) / BM, n_tiles = (p.N + BN - 1) / BN;
-  const int num_tiles = m_tiles * n_tiles;
+  int m_tiles = (p.M + BM - 1) / BM;
+  const int n_tiles = (p.N + BN - 1) / BN;
   const int n_k = (p.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -181,7 +193,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot_ptr;
 
-  pdl_wait();  // x comes from the kernel before this one
+  pdl_wait();  // x (and the list of tiles) comes from the kernels before this one
+  if (p.tiles) m_tiles = min(max(p.meta[0], 0), p.max_row_tiles);
+  const int num_tiles = m_tiles * n_tiles;
+  // tile t: row tile t % m_tiles, column tile t / m_tiles; grouped: the row tile names its expert, whose
+  // matrix starts at row expert * N of W
+  auto tile_at = [&](int t, int& m0, int& n0, int& w0, int& rows) {
+    const int rt = t % m_tiles;
+    n0 = (t / m_tiles) * BN;
+    if (p.tiles) {
+      const int e = p.tiles[3 * rt];
+      m0 = p.tiles[3 * rt + 1];
+      rows = p.tiles[3 * rt + 2];
+      w0 = e * p.N + n0;
+    } else {
+      m0 = rt * BM;
+      rows = p.M - m0;
+      w0 = n0;
+    }
+  };
 
   if (warp == 0) {
     if (lane == 0) {
@@ -189,7 +219,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       int g = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        const int m0 = (t % m_tiles) * BM, n0 = (t / m_tiles) * BN;
+        int m0, n0, w0, rows;
+        tile_at(t, m0, n0, w0, rows);
         for (int it = 0; it < n_k; ++it, ++g) {
           const int s = g % STAGES;
           if (g >= STAGES && !mbar_wait(empty0 + 8 * s, ((g / STAGES) - 1) & 1, p.err)) {
@@ -199,7 +230,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
           const uint32_t a_dst = smem + s * STAGE_BYTES, b_dst = a_dst + A_BYTES;
           mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
           tma_load_2d(a_dst, &map_x, it * BK, m0, full0 + 8 * s);
-          tma_load_2d(b_dst, &map_w, it * BK, n0, full0 + 8 * s);
+          tma_load_2d(b_dst, &map_w, it * BK, w0, full0 + 8 * s);
         }
       }
     }
@@ -235,8 +266,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     int j = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++j) {
       const int b = j & 1;
-      const int m0 = (t % m_tiles) * BM, n0 = (t / m_tiles) * BN;
-      const int row = m0 + q * 32 + lane;
+      int m0, n0, w0, rows;
+      tile_at(t, m0, n0, w0, rows);
+      const bool row_ok = q * 32 + lane < rows;
+      int row = m0 + q * 32 + lane;
+      if (p.scatter && row_ok) row = p.scatter[row];
       if (!mbar_wait(acc_full0 + 8 * b, (j >> 1) & 1, p.err)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
@@ -245,7 +279,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * BN + c0), r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         const int col = n0 + c0;
-        if (row >= p.M || col >= p.N) continue;
+        if (!row_ok || col >= p.N) continue;
+        if (p.mode == 5) {
+          float* dst = reinterpret_cast<float*>(p.out) + (size_t)row * p.ldo + col;
+          if (col + 32 <= p.N) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4)
+              *reinterpret_cast<float4*>(dst + i) = make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]), __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+          } else {
+            for (int i = 0; i < 32; ++i)
+              if (col + i < p.N) dst[i] = __uint_as_float(r[i]);
+          }
+          continue;
+        }
+        if (p.mode == 4) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float z = __uint_as_float(r[i]);
+            r[i] = __float_as_uint(0.5f * z * (1.f + erff(z * 0.70710678118654752440f)));
+          }
+        }
         if (p.mode == 3) {
           // columns are weight rows [g0..7, u0..7, g8..15, u8..15]: 16 outputs from 32 columns
           bf16* dst = reinterpret_cast<bf16*>(p.out) + (size_t)row * p.ldo + (col >> 1);
@@ -340,7 +393,7 @@ int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, const TcParams& p, c
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
       sms = 148;
   }
-  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  const int tiles = (p.tiles ? p.max_row_tiles : (p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
   dim3 grid(tiles < sms ? tiles : sms);
   return launch(kern, grid, dim3(THREADS), smem, st, mx, mw, p);
 }
@@ -360,6 +413,7 @@ KVF_API int kvf_gemm_tcgen05_bf16(const void* x, const void* w, void* out, int M
   if (mode == 3 && (N & 15)) return (int)cudaErrorInvalidValue;
   TcParams p;
   p.out = out; p.M = M; p.N = N; p.K = K; p.ldo = ldo; p.mode = mode; p.err = err;
+  p.tiles = nullptr; p.meta = nullptr; p.scatter = nullptr; p.max_row_tiles = 0;
   CUtensorMap mx, mw;
   int rc = make_map(&mx, x, M, K, ldx, BM);
   if (rc) return rc;
@@ -369,6 +423,32 @@ KVF_API int kvf_gemm_tcgen05_bf16(const void* x, const void* w, void* out, int M
     return launch_tc<256, 4>(mx, mw, p, st);
   }
   rc = make_map(&mw, w, N, K, ldw, 128);
+  if (rc) return rc;
+  return launch_tc<128, 4>(mx, mw, p, st);
+}
+
+// The grouped form: x [P, K] with its rows ordered by expert, w [E * N, K], `tiles` / `meta` as a sort on the device
+// left them (row tiles of at most 128 rows, at most max_row_tiles of them).  gelu != 0: out bfloat16 [P, N] =
+// gelu(x w[e]^T) in the order of x; else out float, row i of the product going to row scatter[i] ([*, N]).
+KVF_API int kvf_gemm_grouped_tcgen05_bf16(const void* x, const void* w, void* out, int P, int N, int K, int E, int ldx,
+                                          int ldo, int gelu, const int* tiles, const int* meta, const int* scatter,
+                                          int max_row_tiles, int* err, cudaStream_t st) {
+  if (P <= 0 || N <= 0 || E <= 0 || max_row_tiles <= 0) return 0;
+  if (K <= 0 || (K & 7) || (ldx & 7) || (ldo & 7) || !tiles || !meta || (!gelu && !scatter)) return (int)cudaErrorInvalidValue;
+  if ((((uintptr_t)x) | ((uintptr_t)w) | ((uintptr_t)out)) & 15) return (int)cudaErrorInvalidValue;
+  if ((long long)E * N > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
+  TcParams p;
+  p.out = out; p.M = P; p.N = N; p.K = K; p.ldo = ldo; p.mode = gelu ? 4 : 5; p.err = err;
+  p.tiles = tiles; p.meta = meta; p.scatter = gelu ? nullptr : scatter; p.max_row_tiles = max_row_tiles;
+  CUtensorMap mx, mw;
+  int rc = make_map(&mx, x, P, K, ldx, BM);
+  if (rc) return rc;
+  if (N >= 256) {
+    rc = make_map(&mw, w, E * N, K, K, 256);
+    if (rc) return rc;
+    return launch_tc<256, 4>(mx, mw, p, st);
+  }
+  rc = make_map(&mw, w, E * N, K, K, 128);
   if (rc) return rc;
   return launch_tc<128, 4>(mx, mw, p, st);
 }

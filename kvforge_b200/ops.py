@@ -53,6 +53,10 @@ _SIGNATURES = {
     "kvf_moe_route_{s}": "plppiiiiiifppp",
     "kvf_moe_experts_{s}": "plppppiiiiippppppp",
     "kvf_moe_max_tiles": "ii",
+    "kvf_moe_sort": "piiipppp",
+    "kvf_moe_gather_bf16": "plpiiipp",
+    "kvf_moe_combine": "pppiiip",
+    "kvf_gemm_grouped_tcgen05_bf16": "pppiiiiiiipppipp",
     "kvf_routed_set_pdl": "i",
 }
 _CTYPES = {"p": ctypes.c_void_p, "i": ctypes.c_int, "l": ctypes.c_longlong, "f": ctypes.c_float}
@@ -1428,14 +1432,21 @@ def moe_route(
     )
 
 
+GROUPED_TILE_ROWS = 128  # rows of a tile of the tensor-memory product
+# from this many rows an expert (on average) the two products of routed experts run on the tcgen05 tensor cores
+GROUPED_TCGEN05_MIN_ROWS = 64
+
+
 def moe_experts(
     x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, scratch: dict, resid: torch.Tensor,
+    err: torch.Tensor | None = None,
 ) -> None:  # fmt: skip
     """``resid[n] += sum_k weights[n, k] * w_down[e] gelu(w_up[e] x[n])`` with ``e = ids[n, k]``: the pairs are
     ordered by expert, every expert's rows go through its two products in tiles, and the results are
     summed per token in the order of ``k``.  ``w_up [E, ff, W]``, ``w_down [E, W, ff]``; ``scratch``: ``order``
     int32 ``[N*top]``, ``tiles`` int32 ``[3*max_tiles]``, ``meta`` int32 ``[4]``, ``act [N*top, ff]``, ``y`` float
-    ``[N*top, W]``.  Four launches."""
+    ``[N*top, W]``, and for many bfloat16 rows ``xs [N*top, W]`` (the pairs' rows side by side by expert).  Four
+    launches, five through the tensor-memory product (``err``: the device flag its bounded waits raise)."""
     s = _suffix(x.dtype)
     _rows2d(x, None, "x")
     _need(w_up, x.dtype, "w_up")
@@ -1456,6 +1467,22 @@ def moe_experts(
     _need(y, torch.float32, "y")
     if order.numel() < n * top or tiles.numel() < 3 * moe_max_tiles(n * top, e) or act.numel() < n * top * ff or y.numel() < n * top * w:
         raise ValueError("moe_experts: a scratch buffer is too small")
+    pairs = n * top
+    xs = scratch.get("xs")
+    if x.dtype == torch.bfloat16 and xs is not None and pairs >= GROUPED_TCGEN05_MIN_ROWS * e and w % 8 == 0 and ff % 8 == 0 and x.stride(0) % 8 == 0:
+        # many rows an expert: both products on the tcgen05 tensor cores, over row tiles of 128 of one expert
+        _need(xs, torch.bfloat16, "xs")
+        if xs.numel() < pairs * w:
+            raise ValueError("moe_experts: a scratch buffer is too small")
+        row_tiles = pairs // GROUPED_TILE_ROWS + e
+        st = _stream()
+        _check(_fn("kvf_moe_sort", ROUTED_LIB)(_ptr(ids), pairs, e, GROUPED_TILE_ROWS, _ptr(order), _ptr(tiles), _ptr(meta), st), "kvf_moe_sort")
+        _check(_fn("kvf_moe_gather_bf16", ROUTED_LIB)(_ptr(x), x.stride(0), _ptr(order), top, pairs, w, _ptr(xs), st), "kvf_moe_gather_bf16")
+        g = _fn("kvf_gemm_grouped_tcgen05_bf16")
+        _check(g(_ptr(xs), _ptr(w_up), _ptr(act), pairs, ff, w, e, w, ff, 1, _ptr(tiles), _ptr(meta), None, row_tiles, _ptr(err), st), "kvf_gemm_grouped_tcgen05_bf16")
+        _check(g(_ptr(act), _ptr(w_down), _ptr(y), pairs, w, ff, e, ff, w, 0, _ptr(tiles), _ptr(meta), _ptr(order), row_tiles, _ptr(err), st), "kvf_gemm_grouped_tcgen05_bf16")
+        _check(_fn("kvf_moe_combine", ROUTED_LIB)(_ptr(resid), _ptr(y), _ptr(weights), n, w, top, st), "kvf_moe_combine")
+        return
     name = f"kvf_moe_experts_{s}"
     _check(
         _fn(name, ROUTED_LIB)(

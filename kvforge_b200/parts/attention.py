@@ -53,8 +53,9 @@ def decode_scratch(rt, ctx, nh: int, nkv: int, d: int, dv: int, tickets: torch.T
     # made for the smallest range size, so that one buffer serves every batch size
     smallest = min(ops.attention_split_size(1, 1, bound), ops.attention_split_size(ops.ATTN_SHORT_RANGE_PAIRS[0], 1, bound))
     sa, sm = ops.attention_scratch_shapes(max(rt.max_seqs, ctx.num_seqs), nh, dv, bound, smallest)
-    acc = rt.buf("attn.part_acc", sa[0] * sa[1] * sa[2], sa[3], torch.float32, cap=0).view(sa)
-    ml = rt.buf("attn.part_ml", sm[0] * sm[1] * sm[2], sm[3], torch.float32, cap=0).view(sm)
+    # a buffer per number of heads (and, by the buffers' key, per value size): layers of other shapes have their own
+    acc = rt.buf(f"attn.part_acc.{nh}", sa[0] * sa[1] * sa[2], sa[3], torch.float32, cap=0).view(sa)
+    ml = rt.buf(f"attn.part_ml.{nh}", sm[0] * sm[1] * sm[2], sm[3], torch.float32, cap=0).view(sm)
     return (acc, ml, tickets), reach, split
 
 

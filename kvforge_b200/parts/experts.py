@@ -74,11 +74,13 @@ class RoutedExperts(FeedForward):
             "act": rt.buf("experts.act", n * top, self.ff, cap=pairs_cap),
             "y": rt.buf("experts.y", n * top, self.hidden, torch.float32, cap=pairs_cap),
         }
+        if x.dtype == torch.bfloat16 and n * top >= ops.GROUPED_TCGEN05_MIN_ROWS * e:
+            scratch["xs"] = rt.buf("experts.xs", n * top, self.hidden, cap=pairs_cap)
         resid = getattr(ctx, "residual", None)
         if resid is not None and resid.shape[0] >= n and resid.shape[1] == self.hidden:
-            ops.moe_experts(x, self.w_up, self.w_down, ids, wts, scratch, resid[:n])
+            ops.moe_experts(x, self.w_up, self.w_down, ids, wts, scratch, resid[:n], rt.err)
             return ops.ADDED
         out = rt.buf("experts.out", n, self.hidden, torch.float32)
         out.zero_()
-        ops.moe_experts(x, self.w_up, self.w_down, ids, wts, scratch, out)
+        ops.moe_experts(x, self.w_up, self.w_down, ids, wts, scratch, out, rt.err)
         return ops.Partials(out.view(1, n, self.hidden))

@@ -196,7 +196,7 @@ def layer_runs(cfg) -> list[tuple[int, int | None]]:
 
 def residual_after_every_run(cfg, w, tokens) -> list[torch.Tensor]:
     eps = cfg["norm"]["eps"]
-    x = w["embed"][torch.as_tensor(tokens, dtype=torch.long)] * cfg["embedding"]["scale"]
+    x = w["embed"][torch.as_tensor(tokens, dtype=torch.long)] * (cfg.get("embedding") or {}).get("scale", 1.0)
     out = []
     for i, step in layer_runs(cfg):
         if step is not None:
