@@ -1,7 +1,9 @@
 // Paged grouped-query attention for bfloat16 on the tensor cores (mma.sync m16n8k16), head
 // sizes 64 and 128.  Same contract as attention_generic.cu: sequence b has ctx_b keys after
 // this step's writes and q_b queries; query i sits at p = ctx_b - q_b + i and sees key j
-// iff j <= p (and j > p - window when window > 0); softmax in float, one rounding.
+// iff j <= p (and j > p - window when window > 0); softmax in float, one rounding.  The tile
+// form also takes, under a window, first keys that stay visible at any distance (j < keep_first)
+// and a bias on the scaled scores by distance and head: bias[bucket[min(p - j, far)]][head].
 //
 // One CTA serves one kv head of one sequence.  The MMA's 16 rows are (query token, head of
 // the group) pairs, so the g query heads that share a kv head share every K/V tile that is
@@ -45,6 +47,11 @@ struct MmaParams {
   int split_size, max_splits;  // max_splits: slices the scratch has room for per (sequence, head)
   int grid_splits;             // ranges that can be non-empty: ceil(longest context / split_size)
   float scale_log2;  // scale * log2(e)
+  // tile form only: first keys that every later query sees, and the bias by distance (null: none)
+  int keep_first;
+  const float* bias;       // [rows][nh]
+  const int* bias_bucket;  // [bias_far + 1]
+  int bias_far;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -168,12 +175,32 @@ __device__ __forceinline__ void pv_tile(float (&o)[D / 8][4], const float (&s)[2
 // (lane/4 and lane/4 + 8) over NT n-tiles whose first key is `key0`.  Row r sees keys
 // lo[r] <= k <= hi[r].  Scores come in as raw dot products and leave as probabilities
 // relative to the new maximum.
-template <int NT, int ND>
+// EXTRA: keys below `keep_first` are seen whatever lo says, and bias[bucket[min(hi[r] - k, far)] * nh + head[r]]
+// is added to the scaled score (hi[r] is the row's own position).
+template <int NT, int ND, bool EXTRA = false>
 __device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&o)[ND][4], float (&m)[2], float (&l)[2],
                                              const int (&lo)[2], const int (&hi)[2], int key0, float scale_log2,
-                                             int lane, bool need_mask) {
+                                             int lane, bool need_mask, int keep_first = 0, const float* bias = nullptr,
+                                             const int* bucket = nullptr, int far = 0, int nh = 0, const int* head = nullptr) {
   float mx[2] = {-INFINITY, -INFINITY};
-  if (need_mask) {  // warp-uniform: only tiles that straddle an edge of what the rows see
+  if (EXTRA) {
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int r = e >> 1;
+        const int kp = key0 + j * 8 + ((lane & 3) << 1) + (e & 1);
+        const bool vis = !need_mask || ((kp <= hi[r]) && (kp >= lo[r] || kp < keep_first));
+        float v = -INFINITY;
+        if (vis) {
+          v = s[j][e] * scale_log2;
+          if (bias) v = fmaf(__ldg(bias + (size_t)__ldg(bucket + min(max(hi[r] - kp, 0), far)) * nh + head[r]), 1.4426950408889634f, v);
+        }
+        s[j][e] = v;
+        mx[r] = fmaxf(mx[r], v);
+      }
+    }
+  } else if (need_mask) {  // warp-uniform: only tiles that straddle an edge of what the rows see
 #pragma unroll
     for (int j = 0; j < NT; ++j) {
 #pragma unroll
@@ -286,13 +313,19 @@ __global__ void __launch_bounds__(NWARPS * 32) attn_mma_tile_kernel(const MmaPar
   loader.init();
   uint32_t qf[D / 16][4];
   load_q_frags<D>(qf, p, q_begin + q0, n_tok, kvh, g, warp * 16, lane);
-  int pos[2], lo[2];
+  int pos[2], lo[2], head[2];
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
-    const int tok = (warp * 16 + (lane >> 2) + 8 * h) / g;
+    const int r = warp * 16 + (lane >> 2) + 8 * h;
+    const int tok = r / g;
     pos[h] = tok < n_tok ? p_first + tok : -1;  // -1: a row past the tile's tokens sees nothing
     lo[h] = p.window > 0 ? pos[h] - p.window + 1 : 0;
+    head[h] = kvh * g + (r - tok * g);
   }
+  // tiles that hold kept first keys and lie wholly before the window's first tile are walked first
+  const int keep = p.window > 0 ? p.keep_first : 0;
+  const int n_keep = min((keep + BN - 1) / BN, kv_lo / BN);
+  const bool extra = keep > 0 || p.bias != nullptr;
   // a warp whose rows all lie past the tile's tokens still helps with the loads
   const bool warp_active = (warp * 16) / g < n_tok;
 
@@ -301,19 +334,20 @@ __global__ void __launch_bounds__(NWARPS * 32) attn_mma_tile_kernel(const MmaPar
   for (int j = 0; j < D / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
-  const int n_tiles = (kv_hi - kv_lo + BN - 1) / BN;
+  const int n_tiles = n_keep + (kv_hi - kv_lo + BN - 1) / BN;
+  auto tile_key0 = [&](int t) { return t < n_keep ? t * BN : kv_lo + (t - n_keep) * BN; };
   // the warp's rows all see every key of a tile that ends at or before the first row's position
   // and starts at or after the last row's window
   const int warp_tok0 = (warp * 16) / g, warp_tok1 = min(n_tok - 1, (warp * 16 + 15) / g);
   const int all_hi = p_first + warp_tok0;  // keys <= this are seen by every valid row of the warp
   const int all_lo = p.window > 0 ? p_first + warp_tok1 - p.window + 1 : 0;
   const bool rows_full = (warp * 16 + 15) / g < n_tok;  // no row of the warp lies past the tile's tokens
-  loader.load(p, bt, kvh, ctx, kv_lo, smem, smem + TILE_BYTES);
+  loader.load(p, bt, kvh, ctx, tile_key0(0), smem, smem + TILE_BYTES);
   cp_async_commit();
   for (int t = 0; t < n_tiles; ++t) {
     const int st = t & 1;
     if (t + 1 < n_tiles) {
-      loader.load(p, bt, kvh, ctx, kv_lo + (t + 1) * BN, smem + (st ^ 1) * 2 * TILE_BYTES,
+      loader.load(p, bt, kvh, ctx, tile_key0(t + 1), smem + (st ^ 1) * 2 * TILE_BYTES,
                   smem + ((st ^ 1) * 2 + 1) * TILE_BYTES);
       cp_async_commit();
       cp_async_wait<1>();
@@ -327,9 +361,13 @@ __global__ void __launch_bounds__(NWARPS * 32) attn_mma_tile_kernel(const MmaPar
 #pragma unroll
       for (int j = 0; j < BN / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
       qk_tile<D, BN / 8>(s, qf, ks, 0, lane);
-      const int key0 = kv_lo + t * BN;
+      const int key0 = tile_key0(t);
       const bool need_mask = !rows_full || key0 + BN - 1 > all_hi || key0 < all_lo;
-      softmax_step<BN / 8, D / 8>(s, o, m, l, lo, pos, key0, p.scale_log2, lane, need_mask);
+      if (extra)
+        softmax_step<BN / 8, D / 8, true>(s, o, m, l, lo, pos, key0, p.scale_log2, lane, need_mask, keep, p.bias, p.bias_bucket,
+                                          p.bias_far, p.nh, head);
+      else
+        softmax_step<BN / 8, D / 8>(s, o, m, l, lo, pos, key0, p.scale_log2, lane, need_mask);
       pv_tile<D, BN / 16>(o, s, vs, 0, lane);
     }
     __syncthreads();  // the stage is free for the load after next
@@ -584,8 +622,11 @@ int launch_mma(const MmaParams& p, int B, int max_q_len, cudaStream_t st) {
 static int run_mma(const void* q, void* out, const void* kcache, const void* vcache, const int* block_tables,
                    const int* qsl, const int* ctx_lens, int B, int max_q_len, int q_stride, int out_stride,
                    int bt_stride, int nh, int nkv, int d, int block_size, float scale, int window, int split_size,
-                   int max_splits, int grid_splits, float* part_acc, float* part_ml, int* tickets, cudaStream_t st) {
+                   int max_splits, int grid_splits, float* part_acc, float* part_ml, int* tickets, cudaStream_t st,
+                   int keep_first = 0, const float* bias = nullptr, const int* bias_bucket = nullptr, int bias_far = 0) {
   if (B <= 0 || max_q_len <= 0) return 0;
+  if ((keep_first > 0 || bias) && split_size > 0) return (int)cudaErrorInvalidValue;  // the tile form's alone
+  if (keep_first < 0 || (bias && (!bias_bucket || bias_far < 0))) return (int)cudaErrorInvalidValue;
   if ((d != 64 && d != 128) || nkv <= 0 || nh % nkv != 0 || block_size <= 0) return (int)cudaErrorInvalidValue;
   const int g = nh / nkv;
   if (g > BM || (unsigned)B > 65535u || (unsigned)nkv > 65535u) return (int)cudaErrorInvalidValue;
@@ -602,6 +643,7 @@ static int run_mma(const void* q, void* out, const void* kcache, const void* vca
   p.split_size = split_size; p.max_splits = max_splits;
   p.grid_splits = grid_splits > 0 && grid_splits < max_splits ? grid_splits : max_splits;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.keep_first = keep_first; p.bias = bias; p.bias_bucket = bias_bucket; p.bias_far = bias_far;
   if (split_size > 0) {
     if (g > 16 || split_size % BN != 0 || max_splits <= 0 || max_splits > 1024 || !part_acc || !part_ml || max_q_len != 1)
       return (int)cudaErrorInvalidValue;
@@ -617,6 +659,17 @@ KVF_API int kvf_paged_attention_mma_bf16(const void* q, void* out, const void* k
                                          cudaStream_t st) {
   return run_mma(q, out, kcache, vcache, block_tables, qsl, ctx_lens, B, max_q_len, q_stride, out_stride, bt_stride, nh,
                  nkv, d, block_size, scale, window, split_size, max_splits, grid_splits, part_acc, part_ml, nullptr, st);
+}
+
+// The tile form with first keys that stay visible under the window and a bias by distance (see the top of this file).
+KVF_API int kvf_paged_attention_mma_biased_bf16(const void* q, void* out, const void* kcache, const void* vcache,
+                                                const int* block_tables, const int* qsl, const int* ctx_lens, int B,
+                                                int max_q_len, int q_stride, int out_stride, int bt_stride, int nh,
+                                                int nkv, int d, int block_size, float scale, int window, int keep_first,
+                                                const float* bias, const int* bias_bucket, int bias_far, cudaStream_t st) {
+  return run_mma(q, out, kcache, vcache, block_tables, qsl, ctx_lens, B, max_q_len, q_stride, out_stride, bt_stride, nh,
+                 nkv, d, block_size, scale, window, 0, 0, 0, nullptr, nullptr, nullptr, st, keep_first, bias, bias_bucket,
+                 bias_far);
 }
 
 // The split form in one launch: `tickets` holds B * nkv counters that are zero before the first

@@ -33,28 +33,47 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
   }
 }
 
-// One warp per token.  Shared memory per warp: scores [E], choice scores [E], group scores [G],
-// group flags [G].
+template <typename T> __device__ __forceinline__ void load8(const T* src, float* dst);
+template <> __device__ __forceinline__ void load8<float>(const float* src, float* dst) {
+  const float4 a = *reinterpret_cast<const float4*>(src), b = *reinterpret_cast<const float4*>(src + 4);
+  dst[0] = a.x; dst[1] = a.y; dst[2] = a.z; dst[3] = a.w; dst[4] = b.x; dst[5] = b.y; dst[6] = b.z; dst[7] = b.w;
+}
+template <> __device__ __forceinline__ void load8<bf16>(const bf16* src, float* dst) {
+  bf16x8_to_float(*reinterpret_cast<const uint4*>(src), dst);
+}
+
+// One CTA of eight warps per token.  The warps share out the experts: a logit is one warp's dot product (a lane adds
+// its products in the order of the columns, then the lanes are summed in a fixed tree), so it does not depend on the
+// batch.  Then the first warp chooses.  Shared memory: scores [E], choice scores [E], group scores [G], group flags [G].
 template <typename T>
-__global__ void __launch_bounds__(128) moe_route_kernel(const T* __restrict__ x, long long x_stride,
+__global__ void __launch_bounds__(256) moe_route_kernel(const T* __restrict__ x, long long x_stride,
                                                          const float* __restrict__ router, const float* __restrict__ correction,
                                                          int n_tokens, int W, int E, int top, int groups, int keep,
-                                                         float norm_eps, int* __restrict__ ids, float* __restrict__ wts) {
+                                                         float norm_eps, int vec, int* __restrict__ ids, float* __restrict__ wts) {
   pdl_launch();
   pdl_wait();
   extern __shared__ float sm[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n = blockIdx.x * 4 + warp;
-  if (n >= n_tokens) return;
-  float* sc = sm + (size_t)warp * (2 * E + 2 * groups);
+  const int n = blockIdx.x;
+  float* sc = sm;
   float* ch = sc + E;
   float* gs = ch + E;
   float* ga = gs + groups;
   const T* row = x + (size_t)n * x_stride;
-  for (int e = 0; e < E; ++e) {
+  for (int e = warp; e < E; e += 8) {
     const float* wr = router + (size_t)e * W;
     float z = 0.f;
-    for (int j = lane; j < W; j += 32) z = fmaf(to_float<T>(row[j]), wr[j], z);
+    if (vec) {
+      for (int j = lane * 8; j < W; j += 256) {
+        float xv[8], wv[8];
+        load8<T>(row + j, xv);
+        load8<float>(wr + j, wv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) z = fmaf(xv[i], wv[i], z);
+      }
+    } else {
+      for (int j = lane; j < W; j += 32) z = fmaf(to_float<T>(row[j]), wr[j], z);
+    }
     z = warp_sum(z);
     if (lane == 0) {
       const float s = 1.f / (1.f + expf(-z));
@@ -62,7 +81,8 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const T* __restrict__ x,
       ch[e] = s + (correction ? correction[e] : 0.f);
     }
   }
-  __syncwarp();
+  __syncthreads();
+  if (warp != 0) return;
   if (groups > 1 && keep < groups) {
     // a group's score: the sum of its two largest choice scores; only the best `keep` groups stay
     const int per = E / groups;
@@ -469,10 +489,11 @@ int run_products<bf16>(const bf16* x, long long x_stride, const bf16* w_up, cons
     if (E <= 0 || top <= 0 || top > E || groups <= 0 || E % groups || keep <= 0 || keep > groups ||                   \
         top > keep * (E / groups))                                                                                    \
       return (int)cudaErrorInvalidValue;                                                                              \
-    const size_t smem = (size_t)4 * (2 * E + 2 * groups) * sizeof(float);                                             \
+    const size_t smem = (size_t)(2 * E + 2 * groups) * sizeof(float);                                                 \
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;                                                          \
-    return launch(moe_route_kernel<T>, dim3((n_tokens + 3) / 4), dim3(128), smem, st, (const T*)x, x_stride, router,  \
-                  correction, n_tokens, W, E, top, groups, keep, norm_eps, ids, wts);                                 \
+    const int vec = (W % 8 == 0) && (x_stride % 8 == 0) && ((((uintptr_t)x) | ((uintptr_t)router)) % 16 == 0);        \
+    return launch(moe_route_kernel<T>, dim3(n_tokens), dim3(256), smem, st, (const T*)x, x_stride, router,            \
+                  correction, n_tokens, W, E, top, groups, keep, norm_eps, vec, ids, wts);                            \
   }                                                                                                                   \
   KVF_API int kvf_moe_experts_##SUF(const void* x, long long x_stride, const void* w_up, const void* w_down,          \
                                     const int* ids, const float* wts, int n_tokens, int W, int ff, int E, int top,    \

@@ -26,6 +26,8 @@ _SIGNATURES = {
     "kvf_cast_from_float_{s}": "pplp",
     "kvf_paged_attention_generic_{s}": "pppppppiiiiiiiiiifiiiippiippip",
     "kvf_paged_attention_mma_bf16": "pppppppiiiiiiiiifiiiippp",
+    "kvf_paged_attention_mma_biased_bf16": "pppppppiiiiiiiiifiippip",
+    "kvf_latent_attention_bf16": "ppppppiiiiiiiiifiiiippp",
     "kvf_paged_attention_tcgen05_bf16": "pppppppiiiiiiiiilfipipp",
     "kvf_paged_attention_decode_fused_bf16": "pppppppiiiiiiiifiiiipppp",
     "kvf_paged_attention_decode_tma_bf16": "pppppppiiiiiiiilfiiiippppiip",
@@ -555,11 +557,16 @@ def paged_attention(
     """
     s = _suffix(q.dtype)
     special = vcache is kcache or keep_first > 0 or bias is not None or d > 256 or (dv or d) > 256
-    if special:
+    # kept first keys and a bias alone, on heads of 64 or 128 in bfloat16 with many queries: the tile form of the mma.sync kernel
+    biased_mma = (
+        special and vcache is not kcache and (dv or d) == d and scratch is None and kernel == "auto"
+        and mma_attention_supported(q.dtype, nh, nkv, d, False) and (q_stride or q.shape[-1]) % 2 == 0 and out.shape[-1] % 2 == 0
+    )  # fmt: skip
+    if special and not biased_mma:
         if kernel not in ("auto", "generic"):
             raise ValueError("only the FP32-pipe attention kernel takes kept first keys, a distance bias, values inside keys or heads wider than 256")
         kernel = "generic"
-    check_head_dim(d, MAX_KEY_DIM if special else 256)
+    check_head_dim(d, MAX_KEY_DIM if special and not biased_mma else 256)
     _need(q, None, "q")
     _need(out, q.dtype, "out")
     _need(kcache, q.dtype, "kcache")
@@ -621,6 +628,17 @@ def paged_attention(
     decode_form = scratch is not None
     use_tc = tcgen05_attention_supported(q.dtype, nh, nkv, d, decode_form) and q_stride % 8 == 0 and out.shape[-1] % 8 == 0 and max_q_len > 1
     use_mma = mma_attention_supported(q.dtype, nh, nkv, d, decode_form)
+    if biased_mma:
+        name = "kvf_paged_attention_mma_biased_bf16"
+        _check(
+            _fn(name)(
+                _ptr(q), _ptr(out), _ptr(kcache), _ptr(vcache), _ptr(block_tables), _ptr(qsl), _ptr(ctx_lens),
+                num_seqs, max_q_len, q_stride, out.shape[-1], bt_stride, nh, nkv, d, block_size, float(scale), int(window),
+                int(keep_first), *bias_args, _stream(),
+            ),
+            name,
+        )  # fmt: skip
+        return
     if kernel == "generic":
         use_tc = use_mma = False
     elif kernel == "tma":
@@ -681,6 +699,56 @@ def paged_attention(
             _ptr(q), _ptr(out), _ptr(kcache), _ptr(vcache), _ptr(block_tables), _ptr(qsl), _ptr(ctx_lens),
             num_seqs, max_q_len, q_stride, out.shape[-1], bt_stride, nh, nkv, d, *((dv,) if not use_mma else ()), block_size, float(scale),
             int(window), split, max_splits, grid_splits, _ptr(pa), _ptr(pm), *(() if use_mma else (int(keep_first), v_stride, *bias_args)), _stream(),
+        ),
+        name,
+        2 if scratch is not None else 1,
+    )  # fmt: skip
+
+
+def latent_attention_supported(dtype: torch.dtype, d: int, dv: int) -> bool:
+    """Whether the tensor-core kernel for a cache of one row per token (``csrc/attention_latent.cu``) takes the shape."""
+    return dtype == torch.bfloat16 and d % 16 == 0 and d <= MAX_KEY_DIM and dv % 32 == 0 and dv // 32 in (2, 3, 4, 8, 16) and dv <= d
+
+
+def latent_attention(
+    q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tensor, qsl: torch.Tensor, ctx_lens: torch.Tensor,
+    num_seqs: int, max_q_len: int, nh: int, d: int, dv: int, scale: float, window: int = 0,
+    scratch: tuple[torch.Tensor, ...] | None = None, max_context: int | None = None, split_size: int = 128,
+) -> None:  # fmt: skip
+    """Attention of a flat batch over a paged cache of ONE row of ``d`` numbers per token (``cache [blocks, 1,
+    block_size, d]``): the row is every head's key and its first ``dv`` numbers every head's value.  ``q [N, nh*d]``,
+    ``out [N, nh*dv]``, bfloat16, on the tensor cores.  With ``scratch`` (partial results ``[B, nh, splits, dv]`` and
+    their maxima and sums ``[B, nh, splits, 2]``, float) and one query a sequence the decode form runs: ranges of
+    ``split_size`` keys in parallel, then a merge."""
+    if not latent_attention_supported(q.dtype, d, dv):
+        raise ValueError("latent_attention: the kernel does not take this shape")
+    _need(q, torch.bfloat16, "q")
+    _need(out, torch.bfloat16, "out")
+    _need(cache, torch.bfloat16, "cache")
+    _need(block_tables, torch.int32, "block_tables")
+    _need(qsl, torch.int32, "query_start_loc")
+    _need(ctx_lens, torch.int32, "context_lens")
+    if cache.dim() != 4 or cache.shape[1] != 1 or cache.shape[3] != d or q.shape[-1] != nh * d or out.shape[-1] != nh * dv:
+        raise ValueError("latent_attention: shapes do not agree")
+    bt_stride = block_tables.shape[-1] if block_tables.dim() == 2 else block_tables.numel() // max(1, num_seqs)
+    split, max_splits, grid_splits, pa, pm = 0, 0, 0, None, None
+    if scratch is not None:
+        pa, pm = scratch[:2]
+        _need(pa, torch.float32, "scratch acc")
+        _need(pm, torch.float32, "scratch ml")
+        if max_q_len != 1 or split_size <= 0 or split_size % 32:
+            raise ValueError("latent_attention: the decode form needs one query per sequence and ranges of a multiple of 32 keys")
+        split, max_splits = split_size, pa.shape[2]
+        if pa.shape[0] < num_seqs or pa.shape[1] != nh or pa.shape[3] != dv:
+            raise ValueError("latent_attention: scratch shape does not fit")
+        if max_context is None or -(-max_context // split) > max_splits:
+            raise ValueError("latent_attention: scratch is too small for the longest context")
+        grid_splits = max(1, -(-max_context // split))
+    name = "kvf_latent_attention_bf16"
+    _check(
+        _fn(name)(
+            _ptr(q), _ptr(out), _ptr(cache), _ptr(block_tables), _ptr(qsl), _ptr(ctx_lens), num_seqs, max_q_len, q.shape[-1], out.shape[-1],
+            bt_stride, nh, d, dv, int(cache.shape[2]), float(scale), int(window), split, max_splits, grid_splits, _ptr(pa), _ptr(pm), _stream(),
         ),
         name,
         2 if scratch is not None else 1,

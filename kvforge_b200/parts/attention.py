@@ -40,7 +40,13 @@ def distance_buckets(rows: int, far: int) -> torch.Tensor:
     return torch.tensor(out, dtype=torch.int32)
 
 
-def decode_scratch(rt, ctx, nh: int, nkv: int, d: int, dv: int, tickets: torch.Tensor | None):
+# keys per range of the decode form on the FP32 pipes when the scores take a bias, the window keeps first keys or the
+# values lie inside wide keys: such a CTA is bound by its arithmetic, not by the bytes it pulls, so ranges are short
+# and many (8 requests of 16 heads over a latent of 576 numbers: 231 us with ranges of 256 keys)
+FP32_PIPE_RANGE = 64
+
+
+def decode_scratch(rt, ctx, nh: int, nkv: int, d: int, dv: int, tickets: torch.Tensor | None, split: int | None = None):
     """What the decode form of attention (key ranges in parallel, then a merge) needs for this step:
     ((partial results, their maxima and sums, tickets), the longest context the grid reaches, keys per
     range).  Buffers are made for the longest context the engine takes; the grid follows the longest
@@ -49,9 +55,14 @@ def decode_scratch(rt, ctx, nh: int, nkv: int, d: int, dv: int, tickets: torch.T
     reach = max(ctx.context_bound if ctx.context_bound > 0 else ctx.max_context_len, 1)
     # 32-bit: one range size whatever the batch, so a request's sums come in the same order beside
     # any number of others; bfloat16: longer ranges for many sequences (fewer CTAs, same bytes)
-    split = ops.attention_split_size(ctx.num_seqs if rt.dtype == torch.bfloat16 else 1, nkv, bound, reach, d)
-    # made for the smallest range size, so that one buffer serves every batch size
-    smallest = min(ops.attention_split_size(1, 1, bound), ops.attention_split_size(ops.ATTN_SHORT_RANGE_PAIRS[0], 1, bound))
+    if split is not None:  # one size whatever the batch (grown only where the longest context would make too many ranges)
+        while -(-bound // split) > ops.MAX_ATTN_SPLITS:
+            split *= 2
+        smallest = split
+    else:
+        split = ops.attention_split_size(ctx.num_seqs if rt.dtype == torch.bfloat16 else 1, nkv, bound, reach, d)
+        # made for the smallest range size, so that one buffer serves every batch size
+        smallest = min(ops.attention_split_size(1, 1, bound), ops.attention_split_size(ops.ATTN_SHORT_RANGE_PAIRS[0], 1, bound))
     sa, sm = ops.attention_scratch_shapes(max(rt.max_seqs, ctx.num_seqs), nh, dv, bound, smallest)
     # a buffer per number of heads (and, by the buffers' key, per value size): layers of other shapes have their own
     acc = rt.buf(f"attn.part_acc.{nh}", sa[0] * sa[1] * sa[2], sa[3], torch.float32, cap=0).view(sa)
@@ -183,7 +194,8 @@ class PagedAttention(Mixer):
             if rt.capturing or rt.graphs_captured:
                 raise RuntimeError("the attention tickets would have to grow after or during graph capture")
             self._tickets = torch.zeros(seqs * self.nkv, dtype=torch.int32, device=rt.device)
-        return decode_scratch(rt, ctx, self.nh, self.nkv, self.d, self.dv, self._tickets)
+        special = self.bias is not None or self.keep_first > 0
+        return decode_scratch(rt, ctx, self.nh, self.nkv, self.d, self.dv, self._tickets, FP32_PIPE_RANGE if special else None)
 
     def forward(self, ctx, x: torch.Tensor, cache) -> torch.Tensor:
         rt = self.rt

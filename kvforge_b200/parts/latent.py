@@ -15,9 +15,14 @@ from __future__ import annotations
 import torch
 
 from .. import ops
-from .attention import decode_scratch
+from .attention import FP32_PIPE_RANGE, decode_scratch
 from .base import CacheNeed, Mixer, PartSpec, WeightDecl, build_part, register_mixer
 from .projection import project
+
+
+# keys per range of the decode form on the tensor cores: a CTA brings its 16 query rows in once per range, so ranges
+# are longer than on the FP32 pipes; still short enough that a few sequences make a few hundred CTAs
+TENSOR_CORE_RANGE = 128
 
 
 @register_mixer("latent_attention")
@@ -134,15 +139,23 @@ class LatentAttention(Mixer):
         # the key up-projection folded into the queries
         self._per_head(y[:, : self.q_cols].view(n, h, dk + dr)[:, :, :dk], self.w_uk, qa.view(n, h, d)[:, :, :r])
         o_lat = rt.buf("latent.o", n, h * r)
+        tensor_cores = ops.latent_attention_supported(qa.dtype, d, r)
         scratch, bound, split = None, None, 256
         if ctx.all_single_query:
-            (acc, ml, _), bound, split = decode_scratch(rt, ctx, h, 1, d, r, None)
+            (acc, ml, _), bound, split = decode_scratch(rt, ctx, h, 1, d, r, None, TENSOR_CORE_RANGE if tensor_cores else FP32_PIPE_RANGE)
             scratch = (acc, ml)
-        ops.paged_attention(
-            qa, o_lat, cache.k, cache.k, ctx.block_tables[cache.group], ctx.query_start_loc, ctx.context_lens, ctx.num_seqs,
-            ctx.max_query_len, h, 1, d, self.scale, window=int(self.window or 0), scratch=scratch, max_context=bound,
-            split_size=split, err=rt.err, dv=r,
-        )  # fmt: skip
+        if tensor_cores:
+            ops.latent_attention(
+                qa, o_lat, cache.k, ctx.block_tables[cache.group], ctx.query_start_loc, ctx.context_lens, ctx.num_seqs, ctx.max_query_len,
+                h, d, r, self.scale, window=int(self.window or 0), scratch=scratch, max_context=bound, split_size=split,
+            )  # fmt: skip
+        else:
+            # 32-bit, or a latent whose size the tensor-core kernel does not take: the FP32 pipes
+            ops.paged_attention(
+                qa, o_lat, cache.k, cache.k, ctx.block_tables[cache.group], ctx.query_start_loc, ctx.context_lens, ctx.num_seqs,
+                ctx.max_query_len, h, 1, d, self.scale, window=int(self.window or 0), scratch=scratch, max_context=bound,
+                split_size=split, err=rt.err, dv=r,
+            )  # fmt: skip
         out = rt.buf("latent.out", n, h * dv)
         self._per_head(o_lat.view(n, h, r), self.w_uv, out.view(n, h, dv))
         if self.gated:

@@ -239,14 +239,17 @@ def step_mixer(part, rt, x, cache_k, cache_v, bs, table, cuts, group_cache):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("window,keep", [(None, 0), (7, 0), (7, 3), (5, 9)])
-def test_attention_with_normed_heads_bias_and_kept_tokens(dtype, window, keep):
+@pytest.mark.parametrize("window,keep", [(None, 0), (7, 0), (7, 3), (5, 9), (70, 66)])
+@pytest.mark.parametrize("dk,dv,t", [(24, 16, 45), (64, 64, 200)])
+def test_attention_with_normed_heads_bias_and_kept_tokens(dtype, window, keep, dk, dv, t):
     """The whole sequence in one step, then portions and single tokens on top of the cache (the decode
-    form: key ranges in parallel), against the plain mixer."""
+    form: key ranges in parallel), against the plain mixer.  Heads of 64 in bfloat16 go to the tensor-core
+    kernel while a step brings more than single tokens; 200 tokens are several of its tiles of keys, with the
+    kept tokens in a tile of their own."""
     from kvforge_b200.parts.base import LayerCache, PartSpec, build_part
 
     rt = runtime(dtype)
-    width, nh, nkv, dk, dv, bs, rows, far, eps = 80, 6, 3, 24, 16, 4, 7, 19, 1e-5
+    width, nh, nkv, bs, rows, far, eps = 80, 6, 3, 4, 7, 19, 1e-5
     m = attention(nh, nkv, dk, dv, rows, far, window, keep)
     names = {"q_proj.weight": "q", "k_proj.weight": "k", "v_proj.weight": "v", "o_proj.weight": "o", "q_norm.weight": "q.norm", "k_norm.weight": "k.norm"}
     part = build_part("mixer", PartSpec("paged_attention", {
@@ -258,26 +261,30 @@ def test_attention_with_normed_heads_bias_and_kept_tokens(dtype, window, keep):
     kinds = type(part).weight_decls(part.params)
     bound = {}
     for local, decl in kinds.items():
-        t = w[names.get(local, local)]
-        bound[local] = t.cuda() if decl.kind == "vector" else t.to(dtype).cuda()
+        tensor = w[names.get(local, local)]
+        bound[local] = tensor.cuda() if decl.kind == "vector" else tensor.to(dtype).cuda()
     part.bind(bound, rt)
-    t = 45
     x = (torch.randn(t, width, generator=g)).to(dtype)
     ref = plain.biased_attention(x.double(), {"m." + k: v.double() for k, v in w.items()}, "m.", m, eps)
-    nb = 16
-    table = [7, 2, 9, 0, 11, 4, 5, 1, 13, 3, 15, 8]
+    nb = 64
+    table = [int(i) for i in torch.randperm(nb, generator=g)]
     need = part.cache_need()
     assert (need.kind, need.keep_first) == (("window", keep) if window else ("full", 0))
     cache = LayerCache(torch.zeros(nb, nkv, bs, dk, device="cuda", dtype=dtype), torch.zeros(nb, nkv, bs, dv, device="cuda", dtype=dtype), 0)
-    for cuts in ([(0, t)], [(0, 17), (17, 19), (19, 20), (20, 21), (21, 34), (34, 35), (35, 36), (36, 45)]):
+    for cuts in ([(0, t)], [(0, 17), (17, 19), (19, 20), (20, 21), (21, 34), (34, 35), (35, 36), (36, t - 3), (t - 3, t - 2), (t - 2, t)]):
         got = step_mixer(part, rt, x, None, None, bs, table, cuts, cache)
         assert rel_rows(got, ref) < part_tol(dtype), cuts
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("heads,dk,dr,dv,rank,window", [(3, 16, 8, 24, 24, 9), (5, 8, 16, 8, 40, None), (2, 32, 32, 16, 264, 30)])
+@pytest.mark.parametrize(
+    "heads,dk,dr,dv,rank,window",
+    [(3, 16, 8, 24, 24, 9), (5, 8, 16, 8, 40, None), (2, 32, 32, 16, 264, 30), (16, 16, 32, 8, 64, 40), (5, 8, 16, 8, 96, None), (20, 8, 16, 8, 128, 33), (2, 32, 64, 16, 512, 70)],
+)
 def test_latent_attention(dtype, heads, dk, dr, dv, rank, window):
-    """The cache holds one row of ``rank + rot_dim`` numbers per token; whole, in portions and token by token."""
+    """The cache holds one row of ``rank + rot_dim`` numbers per token; whole, in portions and token by token.  In
+    bfloat16 latents of 64, 96, 128, 256 or 512 numbers (with rows that are a multiple of 16 wide) go to the
+    tensor-core kernel: 16 heads a CTA, fewer heads with several tokens a CTA, more heads in chunks."""
     from kvforge_b200.parts.base import LayerCache, PartSpec, build_part
 
     rt = runtime(dtype)
@@ -293,15 +300,15 @@ def test_latent_attention(dtype, heads, dk, dr, dv, rank, window):
     w = {k: (torch.randn(s, generator=g) * (2.0 / s[-1] ** 0.5) + (1.0 if "norm" in k else 0.0)).to(dtype).float() for k, s in shapes.items()}
     kinds = type(part).weight_decls(part.params)
     part.bind({k: (w[k].cuda() if kinds[k].kind == "vector" else w[k].to(dtype).cuda()) for k in kinds}, rt)
-    t = 50
+    t = 50 if rank < 64 else 150
     x = torch.randn(t, width, generator=g).to(dtype)
     ref = plain.latent_attention(x.double(), {"m." + k: v.double() for k, v in w.items()}, "m.", m, eps)
     need = part.cache_need()
     assert need.v_in_k and need.kv_heads == 1 and need.head_dim == rank + dr and need.value_dim == rank
-    table = [6, 1, 4, 0, 7, 2, 5, 3]
-    k = torch.zeros(8, 1, bs, rank + dr, device="cuda", dtype=dtype)
+    table = [int(i) for i in torch.randperm(24, generator=g)]
+    k = torch.zeros(24, 1, bs, rank + dr, device="cuda", dtype=dtype)
     cache = LayerCache(k, k, 0)
-    for cuts in ([(0, t)], [(0, 21), (21, 23), (23, 24), (24, 25), (25, 41), (41, 42), (42, 50)]):
+    for cuts in ([(0, t)], [(0, 21), (21, 23), (23, 24), (24, 25), (25, 41), (41, 42), (42, t - 2), (t - 2, t - 1), (t - 1, t)]):
         got = step_mixer(part, rt, x, None, None, bs, table, cuts, cache)
         assert rel_rows(got, ref) < part_tol(dtype), cuts
 
