@@ -2,7 +2,7 @@
 // sizes 64 and 128.  Same contract as attention_generic.cu: sequence b has ctx_b keys after
 // this step's writes and q_b queries; query i sits at p = ctx_b - q_b + i and sees key j
 // iff j <= p (and j > p - window when window > 0); softmax in float, one rounding.  The tile
-// form also takes, under a window, first keys that stay visible at any distance (j < keep_first)
+// Both forms also take, under a window, first keys that stay visible at any distance (j < keep_first)
 // and a bias on the scaled scores by distance and head: bias[bucket[min(p - j, far)]][head].
 //
 // One CTA serves one kv head of one sequence.  The MMA's 16 rows are (query token, head of
@@ -47,7 +47,7 @@ struct MmaParams {
   int split_size, max_splits;  // max_splits: slices the scratch has room for per (sequence, head)
   int grid_splits;             // ranges that can be non-empty: ceil(longest context / split_size)
   float scale_log2;  // scale * log2(e)
-  // tile form only: first keys that every later query sees, and the bias by distance (null: none)
+  // first keys that every later query sees, and the bias by distance (null: none)
   int keep_first;
   const float* bias;       // [rows][nh]
   const int* bias_bucket;  // [bias_far + 1]
@@ -175,13 +175,14 @@ __device__ __forceinline__ void pv_tile(float (&o)[D / 8][4], const float (&s)[2
 // (lane/4 and lane/4 + 8) over NT n-tiles whose first key is `key0`.  Row r sees keys
 // lo[r] <= k <= hi[r].  Scores come in as raw dot products and leave as probabilities
 // relative to the new maximum.
-// EXTRA: keys below `keep_first` are seen whatever lo says, and bias[bucket[min(hi[r] - k, far)] * nh + head[r]]
-// is added to the scaled score (hi[r] is the row's own position).
+// EXTRA: keys below `keep_first` are seen whatever lo says, and bias[bucket[min(qpos[r] - k, far)] * nh + head[r]]
+// is added to the scaled score (qpos[r] is the row's own position).
 template <int NT, int ND, bool EXTRA = false>
 __device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&o)[ND][4], float (&m)[2], float (&l)[2],
                                              const int (&lo)[2], const int (&hi)[2], int key0, float scale_log2,
                                              int lane, bool need_mask, int keep_first = 0, const float* bias = nullptr,
-                                             const int* bucket = nullptr, int far = 0, int nh = 0, const int* head = nullptr) {
+                                             const int* bucket = nullptr, int far = 0, int nh = 0, const int* head = nullptr,
+                                             const int* qpos = nullptr) {
   float mx[2] = {-INFINITY, -INFINITY};
   if (EXTRA) {
 #pragma unroll
@@ -194,7 +195,7 @@ __device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&o)[ND][4
         float v = -INFINITY;
         if (vis) {
           v = s[j][e] * scale_log2;
-          if (bias) v = fmaf(__ldg(bias + (size_t)__ldg(bucket + min(max(hi[r] - kp, 0), far)) * nh + head[r]), 1.4426950408889634f, v);
+          if (bias) v = fmaf(__ldg(bias + (size_t)__ldg(bucket + min(max(qpos[r] - kp, 0), far)) * nh + head[r]), 1.4426950408889634f, v);
         }
         s[j][e] = v;
         mx[r] = fmaxf(mx[r], v);
@@ -365,7 +366,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attn_mma_tile_kernel(const MmaPar
       const bool need_mask = !rows_full || key0 + BN - 1 > all_hi || key0 < all_lo;
       if (extra)
         softmax_step<BN / 8, D / 8, true>(s, o, m, l, lo, pos, key0, p.scale_log2, lane, need_mask, keep, p.bias, p.bias_bucket,
-                                          p.bias_far, p.nh, head);
+                                          p.bias_far, p.nh, head, pos);
       else
         softmax_step<BN / 8, D / 8>(s, o, m, l, lo, pos, key0, p.scale_log2, lane, need_mask);
       pv_tile<D, BN / 16>(o, s, vs, 0, lane);
@@ -410,16 +411,22 @@ __global__ void __launch_bounds__(NWARPS * 32) attn_mma_split_kernel(const MmaPa
   const int kv_hi = min(ctx, kv_lo + p.split_size);
   const int key_lo = kv_lo;
   if (p.window > 0) kv_lo = max(kv_lo, (max(0, ctx - p.window) / BN) * BN);
-  const bool empty = kv_lo >= kv_hi;  // wholly before the window
+  // tiles of the range that hold kept first keys and lie before the window's first tile are walked first
+  const int keep = p.window > 0 ? p.keep_first : 0;
+  const int keep_hi = min(min(kv_hi, kv_lo), ((keep + BN - 1) / BN) * BN);
+  const int n_keep = keep_hi > key_lo ? (keep_hi - key_lo + BN - 1) / BN : 0;
+  const bool extra = keep > 0 || p.bias != nullptr;
+  const bool empty = kv_lo >= kv_hi && n_keep == 0;  // wholly before the window, and no kept key
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int* bt = p.block_tables + (size_t)b * p.bt_stride;
   TileLoader<D> loader;
   loader.init();
-  const int n_tiles = (live && !empty) ? (kv_hi - kv_lo + BN - 1) / BN : 0;
+  const int n_tiles = (live && !empty) ? n_keep + (kv_hi > kv_lo ? (kv_hi - kv_lo + BN - 1) / BN : 0) : 0;
+  auto tile_key0 = [&](int t) { return t < n_keep ? key_lo + t * BN : kv_lo + (t - n_keep) * BN; };
   int issued = 0;
   if (n_tiles > 0 && kv_hi < ctx) {
     for (; issued < 2 && issued < n_tiles; ++issued) {
-      loader.load(p, bt, kvh, kv_hi, kv_lo + issued * BN, smem + issued * 2 * TILE_BYTES, smem + (issued * 2 + 1) * TILE_BYTES);
+      loader.load(p, bt, kvh, kv_hi, tile_key0(issued), smem + issued * 2 * TILE_BYTES, smem + (issued * 2 + 1) * TILE_BYTES);
       cp_async_commit();
     }
   }
@@ -453,6 +460,8 @@ __global__ void __launch_bounds__(NWARPS * 32) attn_mma_split_kernel(const MmaPa
   const int first_seen = max(key_lo, p.window > 0 ? ctx - p.window : 0);
   const int lo[2] = {first_seen, first_seen};
   const int hi[2] = {kv_hi - 1, kv_hi - 1};
+  const int qpos[2] = {ctx - 1, ctx - 1};
+  const int head[2] = {min(kvh * g + (lane >> 2), p.nh - 1), min(kvh * g + (lane >> 2) + 8, p.nh - 1)};
 
   float o[D / 8][4];
 #pragma unroll
@@ -460,14 +469,14 @@ __global__ void __launch_bounds__(NWARPS * 32) attn_mma_split_kernel(const MmaPa
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
   if (issued == 0) {
-    loader.load(p, bt, kvh, kv_hi, kv_lo, smem, smem + TILE_BYTES);
+    loader.load(p, bt, kvh, kv_hi, tile_key0(0), smem, smem + TILE_BYTES);
     cp_async_commit();
     issued = 1;
   }
   for (int t = 0; t < n_tiles; ++t) {
     const int st = t & 1;
     if (issued == t + 1 && t + 1 < n_tiles) {  // its stage was read in iteration t-1
-      loader.load(p, bt, kvh, kv_hi, kv_lo + (t + 1) * BN, smem + (st ^ 1) * 2 * TILE_BYTES,
+      loader.load(p, bt, kvh, kv_hi, tile_key0(t + 1), smem + (st ^ 1) * 2 * TILE_BYTES,
                   smem + ((st ^ 1) * 2 + 1) * TILE_BYTES);
       cp_async_commit();
       ++issued;
@@ -483,9 +492,13 @@ __global__ void __launch_bounds__(NWARPS * 32) attn_mma_split_kernel(const MmaPa
       s[0][0] = s[0][1] = s[0][2] = s[0][3] = 0.f;
       s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
       qk_tile<D, 2>(s, qf, ks, 2 * warp, lane);  // this warp's 16 keys of the tile
-      const int key0 = kv_lo + t * BN + warp * 16;
+      const int key0 = tile_key0(t) + warp * 16;
       const bool need_mask = key0 < first_seen || key0 + 15 > kv_hi - 1;
-      softmax_step<2, D / 8>(s, o, m, l, lo, hi, key0, p.scale_log2, lane, need_mask);
+      if (extra)
+        softmax_step<2, D / 8, true>(s, o, m, l, lo, hi, key0, p.scale_log2, lane, need_mask, keep, p.bias, p.bias_bucket, p.bias_far,
+                                     p.nh, head, qpos);
+      else
+        softmax_step<2, D / 8>(s, o, m, l, lo, hi, key0, p.scale_log2, lane, need_mask);
       pv_tile<D, 1>(o, s, vs, warp, lane);
     }
     __syncthreads();
@@ -625,7 +638,6 @@ static int run_mma(const void* q, void* out, const void* kcache, const void* vca
                    int max_splits, int grid_splits, float* part_acc, float* part_ml, int* tickets, cudaStream_t st,
                    int keep_first = 0, const float* bias = nullptr, const int* bias_bucket = nullptr, int bias_far = 0) {
   if (B <= 0 || max_q_len <= 0) return 0;
-  if ((keep_first > 0 || bias) && split_size > 0) return (int)cudaErrorInvalidValue;  // the tile form's alone
   if (keep_first < 0 || (bias && (!bias_bucket || bias_far < 0))) return (int)cudaErrorInvalidValue;
   if ((d != 64 && d != 128) || nkv <= 0 || nh % nkv != 0 || block_size <= 0) return (int)cudaErrorInvalidValue;
   const int g = nh / nkv;
@@ -672,6 +684,15 @@ KVF_API int kvf_paged_attention_mma_biased_bf16(const void* q, void* out, const 
                  bias_far);
 }
 
+// The split form in one launch (see below) with kept first keys and a bias by distance.
+KVF_API int kvf_paged_attention_decode_biased_bf16(const void* q, void* out, const void* kcache, const void* vcache,
+                                                   const int* block_tables, const int* qsl, const int* ctx_lens, int B,
+                                                   int q_stride, int out_stride, int bt_stride, int nh, int nkv, int d,
+                                                   int block_size, float scale, int window, int split_size,
+                                                   int max_splits, int grid_splits, float* part_acc, float* part_ml,
+                                                   int* tickets, int keep_first, const float* bias, const int* bias_bucket,
+                                                   int bias_far, cudaStream_t st);
+
 // The split form in one launch: `tickets` holds B * nkv counters that are zero before the first
 // launch (each launch leaves them zero); the CTA that finishes last among the ranges of a
 // (sequence, kv head) merges them.  Launches that share `tickets` must not overlap.
@@ -684,4 +705,17 @@ KVF_API int kvf_paged_attention_decode_fused_bf16(const void* q, void* out, cons
   if (!tickets || split_size <= 0) return (int)cudaErrorInvalidValue;
   return run_mma(q, out, kcache, vcache, block_tables, qsl, ctx_lens, B, 1, q_stride, out_stride, bt_stride, nh, nkv, d,
                  block_size, scale, window, split_size, max_splits, grid_splits, part_acc, part_ml, tickets, st);
+}
+
+KVF_API int kvf_paged_attention_decode_biased_bf16(const void* q, void* out, const void* kcache, const void* vcache,
+                                                   const int* block_tables, const int* qsl, const int* ctx_lens, int B,
+                                                   int q_stride, int out_stride, int bt_stride, int nh, int nkv, int d,
+                                                   int block_size, float scale, int window, int split_size,
+                                                   int max_splits, int grid_splits, float* part_acc, float* part_ml,
+                                                   int* tickets, int keep_first, const float* bias, const int* bias_bucket,
+                                                   int bias_far, cudaStream_t st) {
+  if (!tickets || split_size <= 0) return (int)cudaErrorInvalidValue;
+  return run_mma(q, out, kcache, vcache, block_tables, qsl, ctx_lens, B, 1, q_stride, out_stride, bt_stride, nh, nkv, d,
+                 block_size, scale, window, split_size, max_splits, grid_splits, part_acc, part_ml, tickets, st, keep_first, bias,
+                 bias_bucket, bias_far);
 }

@@ -42,9 +42,12 @@ template <> __device__ __forceinline__ void load8<bf16>(const bf16* src, float* 
   bf16x8_to_float(*reinterpret_cast<const uint4*>(src), dst);
 }
 
-// One CTA of eight warps per token.  The warps share out the experts: a logit is one warp's dot product (a lane adds
-// its products in the order of the columns, then the lanes are summed in a fixed tree), so it does not depend on the
-// batch.  Then the first warp chooses.  Shared memory: scores [E], choice scores [E], group scores [G], group flags [G].
+// One CTA of eight warps per RT tokens.  The warps share out the experts: a logit is one warp's dot product (a lane
+// adds its products in the order of the columns, then the lanes are summed in a fixed tree), so it does not depend on
+// the batch; a row of the router is read once for the CTA's tokens.  Then warp t chooses for token t.  Shared memory
+// per token: scores [E], choice scores [E], group scores [G], group flags [G].
+constexpr int RT = 4;
+
 template <typename T>
 __global__ void __launch_bounds__(256) moe_route_kernel(const T* __restrict__ x, long long x_stride,
                                                          const float* __restrict__ router, const float* __restrict__ correction,
@@ -54,35 +57,51 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const T* __restrict__ x,
   pdl_wait();
   extern __shared__ float sm[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n = blockIdx.x;
-  float* sc = sm;
-  float* ch = sc + E;
-  float* gs = ch + E;
-  float* ga = gs + groups;
-  const T* row = x + (size_t)n * x_stride;
+  const int n0 = blockIdx.x * RT;
+  const int per_token = 2 * E + 2 * groups;
   for (int e = warp; e < E; e += 8) {
     const float* wr = router + (size_t)e * W;
-    float z = 0.f;
+    float z[RT];
+#pragma unroll
+    for (int t = 0; t < RT; ++t) z[t] = 0.f;
     if (vec) {
       for (int j = lane * 8; j < W; j += 256) {
-        float xv[8], wv[8];
-        load8<T>(row + j, xv);
+        float wv[8];
         load8<float>(wr + j, wv);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) z = fmaf(xv[i], wv[i], z);
+        for (int t = 0; t < RT; ++t) {
+          if (n0 + t >= n_tokens) break;
+          float xv[8];
+          load8<T>(x + (size_t)(n0 + t) * x_stride + j, xv);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) z[t] = fmaf(xv[i], wv[i], z[t]);
+        }
       }
     } else {
-      for (int j = lane; j < W; j += 32) z = fmaf(to_float<T>(row[j]), wr[j], z);
+      for (int j = lane; j < W; j += 32) {
+        const float wv = wr[j];
+#pragma unroll
+        for (int t = 0; t < RT; ++t)
+          if (n0 + t < n_tokens) z[t] = fmaf(to_float<T>(x[(size_t)(n0 + t) * x_stride + j]), wv, z[t]);
+      }
     }
-    z = warp_sum(z);
-    if (lane == 0) {
-      const float s = 1.f / (1.f + expf(-z));
-      sc[e] = s;
-      ch[e] = s + (correction ? correction[e] : 0.f);
+#pragma unroll
+    for (int t = 0; t < RT; ++t) {
+      const float zt = warp_sum(z[t]);
+      if (lane == 0) {
+        const float s = 1.f / (1.f + expf(-zt));
+        sm[t * per_token + e] = s;
+        sm[t * per_token + E + e] = s + (correction ? correction[e] : 0.f);
+      }
     }
   }
   __syncthreads();
-  if (warp != 0) return;
+  if (warp >= RT || n0 + warp >= n_tokens) return;
+  const int n = n0 + warp;
+  float* sc = sm + warp * per_token;
+  float* ch = sc + E;
+  float* gs = ch + E;
+  float* ga = gs + groups;
   if (groups > 1 && keep < groups) {
     // a group's score: the sum of its two largest choice scores; only the best `keep` groups stay
     const int per = E / groups;
@@ -430,6 +449,30 @@ __global__ void moe_combine_kernel(float* __restrict__ resid, const float* __res
                                    long long total, int W, int top) {
   pdl_launch();
   pdl_wait();
+  if ((W & 3) == 0) {  // four columns a thread; each column's sum is the same chain over k as below
+    const int w4 = W >> 2;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < (total >> 2); idx += (long long)gridDim.x * blockDim.x) {
+      const long long n = idx / w4;
+      const int c = (int)(idx - n * w4) * 4;
+      float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int k = 0; k < top; ++k) {
+        const float g = wts[n * top + k];
+        const float4 v = *reinterpret_cast<const float4*>(y + ((size_t)n * top + k) * W + c);
+        s.x = fmaf(g, v.x, s.x);
+        s.y = fmaf(g, v.y, s.y);
+        s.z = fmaf(g, v.z, s.z);
+        s.w = fmaf(g, v.w, s.w);
+      }
+      float4* r = reinterpret_cast<float4*>(resid + (size_t)n * W + c);
+      float4 o = *r;
+      o.x += s.x;
+      o.y += s.y;
+      o.z += s.z;
+      o.w += s.w;
+      *r = o;
+    }
+    return;
+  }
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
     const long long n = idx / W;
     const int c = (int)(idx - n * W);
@@ -489,10 +532,10 @@ int run_products<bf16>(const bf16* x, long long x_stride, const bf16* w_up, cons
     if (E <= 0 || top <= 0 || top > E || groups <= 0 || E % groups || keep <= 0 || keep > groups ||                   \
         top > keep * (E / groups))                                                                                    \
       return (int)cudaErrorInvalidValue;                                                                              \
-    const size_t smem = (size_t)(2 * E + 2 * groups) * sizeof(float);                                                 \
+    const size_t smem = (size_t)RT * (2 * E + 2 * groups) * sizeof(float);                                            \
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;                                                          \
     const int vec = (W % 8 == 0) && (x_stride % 8 == 0) && ((((uintptr_t)x) | ((uintptr_t)router)) % 16 == 0);        \
-    return launch(moe_route_kernel<T>, dim3(n_tokens), dim3(256), smem, st, (const T*)x, x_stride, router,            \
+    return launch(moe_route_kernel<T>, dim3((n_tokens + RT - 1) / RT), dim3(256), smem, st, (const T*)x, x_stride, router, \
                   correction, n_tokens, W, E, top, groups, keep, norm_eps, vec, ids, wts);                            \
   }                                                                                                                   \
   KVF_API int kvf_moe_experts_##SUF(const void* x, long long x_stride, const void* w_up, const void* w_down,          \

@@ -28,6 +28,7 @@ _SIGNATURES = {
     "kvf_paged_attention_mma_bf16": "pppppppiiiiiiiiifiiiippp",
     "kvf_paged_attention_mma_biased_bf16": "pppppppiiiiiiiiifiippip",
     "kvf_latent_attention_bf16": "ppppppiiiiiiiiifiiiippp",
+    "kvf_paged_attention_decode_biased_bf16": "pppppppiiiiiiiifiiiipppippip",
     "kvf_paged_attention_tcgen05_bf16": "pppppppiiiiiiiiilfipipp",
     "kvf_paged_attention_decode_fused_bf16": "pppppppiiiiiiiifiiiipppp",
     "kvf_paged_attention_decode_tma_bf16": "pppppppiiiiiiiilfiiiippppiip",
@@ -559,8 +560,9 @@ def paged_attention(
     special = vcache is kcache or keep_first > 0 or bias is not None or d > 256 or (dv or d) > 256
     # kept first keys and a bias alone, on heads of 64 or 128 in bfloat16 with many queries: the tile form of the mma.sync kernel
     biased_mma = (
-        special and vcache is not kcache and (dv or d) == d and scratch is None and kernel == "auto"
-        and mma_attention_supported(q.dtype, nh, nkv, d, False) and (q_stride or q.shape[-1]) % 2 == 0 and out.shape[-1] % 2 == 0
+        special and vcache is not kcache and (dv or d) == d and kernel == "auto"
+        and mma_attention_supported(q.dtype, nh, nkv, d, scratch is not None) and (q_stride or q.shape[-1]) % 2 == 0 and out.shape[-1] % 2 == 0
+        and (scratch is None or len(scratch) > 2)
     )  # fmt: skip
     if special and not biased_mma:
         if kernel not in ("auto", "generic"):
@@ -628,6 +630,17 @@ def paged_attention(
     decode_form = scratch is not None
     use_tc = tcgen05_attention_supported(q.dtype, nh, nkv, d, decode_form) and q_stride % 8 == 0 and out.shape[-1] % 8 == 0 and max_q_len > 1
     use_mma = mma_attention_supported(q.dtype, nh, nkv, d, decode_form)
+    if biased_mma and scratch is not None:
+        name = "kvf_paged_attention_decode_biased_bf16"
+        _check(
+            _fn(name)(
+                _ptr(q), _ptr(out), _ptr(kcache), _ptr(vcache), _ptr(block_tables), _ptr(qsl), _ptr(ctx_lens),
+                num_seqs, q_stride, out.shape[-1], bt_stride, nh, nkv, d, block_size, float(scale),
+                int(window), split, max_splits, grid_splits, _ptr(pa), _ptr(pm), _ptr(tickets), int(keep_first), *bias_args, _stream(),
+            ),
+            name,
+        )  # fmt: skip
+        return
     if biased_mma:
         name = "kvf_paged_attention_mma_biased_bf16"
         _check(
