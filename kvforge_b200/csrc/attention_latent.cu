@@ -5,8 +5,9 @@
 // has ctx_b rows after this step's writes and q_b queries; query i sits at p = ctx_b - q_b + i and sees
 // row j iff j <= p (and j > p - window when window > 0); scores and softmax in float, one rounding.
 //
-// A CTA of four warps owns 16 rows of (query token, head): all 16 heads of one token, or several
-// tokens of fewer heads, so that a tile of keys brought into shared memory serves every head.  Keys come
+// A CTA of four warps owns 16 or 32 rows of (query token, head): all 16 heads of one or two tokens, or
+// several tokens of fewer heads, so that a tile of keys brought into shared memory serves every head
+// (32 rows where a step brings enough tokens: a tile is then fetched, and the warps meet, half as often).  Keys come
 // in tiles of 32 that start at multiples of 32 (cp.async, two stages, rows padded by 16 bytes so that
 // the 8 rows of an ldmatrix lie in different banks).  Per tile:
 //   scores   the four warps share out the k-steps of q . k (d/16 of them), leave their partial
@@ -26,7 +27,7 @@ namespace {
 
 constexpr int BN = 32;     // keys per tile
 constexpr int WARPS = 4;
-constexpr int ROWS = 16;   // (token, head) rows per CTA
+constexpr int ROWS = 16;   // (token, head) rows of one m-tile; a CTA has MT of them
 constexpr int PAD = 8;     // elements of padding per row of shared memory
 
 struct LatParams {
@@ -41,6 +42,7 @@ struct LatParams {
   int q_stride, out_stride, bt_stride;
   int nh, d, dv, block_size;
   int gh, chunks, tq;  // heads per CTA, head chunks, tokens per CTA
+  int bs_shift;        // log2(block_size) if it is a power of two, else -1
   int window;
   int split_size, max_splits;
   float scale_log2;  // scale * log2(e)
@@ -76,18 +78,19 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
-// NTW: n-tiles of 8 output columns per warp (dv = 32 * NTW).
-template <int NTW, bool SPLIT>
+// NTW: n-tiles of 8 output columns per warp (dv = 32 * NTW).  MT: m-tiles of 16 rows per CTA.
+template <int NTW, int MT, bool SPLIT>
 __global__ void __launch_bounds__(WARPS * 32) latent_attn_kernel(const LatParams p) {
   pdl_launch();
   pdl_wait();
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const int d = p.d, ld = d + PAD;  // elements per row of shared memory
   const uint32_t row_bytes = (uint32_t)ld * 2;
-  const uint32_t qs = su32(smem_raw);                       // [ROWS][ld]
-  const uint32_t ks0 = qs + ROWS * row_bytes;               // [2][BN][ld]
+  constexpr int RWS = ROWS * MT;
+  const uint32_t qs = su32(smem_raw);                       // [RWS][ld]
+  const uint32_t ks0 = qs + RWS * row_bytes;                // [2][BN][ld]
   const uint32_t k_stage = BN * row_bytes;
-  float* sp = reinterpret_cast<float*>(smem_raw + (size_t)(ROWS + 2 * BN) * row_bytes);  // [WARPS][4][4][32]
+  float* sp = reinterpret_cast<float*>(smem_raw + (size_t)(RWS + 2 * BN) * row_bytes);  // [WARPS][MT][4][4][32]
 
   const int b = blockIdx.y, chunk = blockIdx.z;
   const int q_begin = p.qsl[b], q_len = p.qsl[b + 1] - q_begin;
@@ -128,7 +131,7 @@ __global__ void __launch_bounds__(WARPS * 32) latent_attn_kernel(const LatParams
 
   // ---- the query rows: row r -> (token r / gh, head chunk * gh + r % gh); rows past the tokens or the heads are zeros
   const int chunks_per_row = d / 8;
-  for (int idx = threadIdx.x; idx < ROWS * chunks_per_row; idx += blockDim.x) {
+  for (int idx = threadIdx.x; idx < RWS * chunks_per_row; idx += blockDim.x) {
     const int r = idx / chunks_per_row, c = idx - r * chunks_per_row;
     const int tok = r / p.gh, hh = chunk * p.gh + (r - tok * p.gh);
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
@@ -138,30 +141,39 @@ __global__ void __launch_bounds__(WARPS * 32) latent_attn_kernel(const LatParams
   }
 
   const int* bt = p.block_tables + (size_t)b * p.bt_stride;
+  // a warp brings 8 keys of a tile, its lanes the 16-byte chunks of a row: the page of a key is looked up once a key
   auto load_tile = [&](int stage, int t0) {
     const uint32_t dst0 = ks0 + stage * k_stage;
-    for (int idx = threadIdx.x; idx < BN * chunks_per_row; idx += blockDim.x) {
-      const int key = idx / chunks_per_row, c = idx - key * chunks_per_row;
+#pragma unroll 2
+    for (int i = 0; i < BN / WARPS; ++i) {
+      const int key = warp * (BN / WARPS) + i;
       const int kp = t0 + key;
-      const int blk = kp < ctx ? bt[kp / p.block_size] : -1;  // a page given back lies outside every window: zeros
+      const int page = p.bs_shift >= 0 ? kp >> p.bs_shift : kp / p.block_size;
+      const int off = p.bs_shift >= 0 ? kp & (p.block_size - 1) : kp - page * p.block_size;
+      const int blk = kp < ctx ? bt[page] : -1;  // a page given back lies outside every window: zeros
       const bool valid = blk >= 0;
-      const bf16* src = p.cache + (valid ? ((size_t)blk * p.block_size + (size_t)(kp % p.block_size)) * d + c * 8 : 0);
-      cpa16(dst0 + key * row_bytes + c * 16, src, valid);
+      const bf16* src = p.cache + (valid ? ((size_t)blk * p.block_size + (size_t)off) * d : 0);
+      const uint32_t dst = dst0 + key * row_bytes;
+      for (int c = lane; c < chunks_per_row; c += 32) cpa16(dst + c * 16, src + (valid ? c * 8 : 0), valid);
     }
   };
 
-  // the two rows a thread holds: lane/4 and lane/4 + 8
-  int pos[2];
+  // the two rows of every m-tile that a thread holds: lane/4 and lane/4 + 8
+  int pos[MT][2];
+  float o[MT][NTW][4], m[MT][2], l[MT][2];
 #pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    const int r = (lane >> 2) + 8 * h;
-    const int tok = r / p.gh, hh = chunk * p.gh + (r - tok * p.gh);
-    pos[h] = (tok < n_tok && hh < p.nh) ? p_first + tok : -1;  // -1: sees nothing
+  for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = mt * ROWS + (lane >> 2) + 8 * h;
+      const int tok = r / p.gh, hh = chunk * p.gh + (r - tok * p.gh);
+      pos[mt][h] = (tok < n_tok && hh < p.nh) ? p_first + tok : -1;  // -1: sees nothing
+      m[mt][h] = -INFINITY;
+      l[mt][h] = 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < NTW; ++j) o[mt][j][0] = o[mt][j][1] = o[mt][j][2] = o[mt][j][3] = 0.f;
   }
-  float o[NTW][4];
-#pragma unroll
-  for (int j = 0; j < NTW; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
-  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
   const int n_ksteps = d / 16;
   const int ks_begin = (warp * n_ksteps) / WARPS, ks_end = ((warp + 1) * n_ksteps) / WARPS;
@@ -181,97 +193,117 @@ __global__ void __launch_bounds__(WARPS * 32) latent_attn_kernel(const LatParams
     __syncthreads();  // the tile (and, the first time, the query rows) are in shared memory
     const uint32_t ks = ks0 + st * k_stage;
     // ---- this warp's share of the k-steps of q . k
-    float s[4][4];
+    float s[MT][4][4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) s[mt][j][0] = s[mt][j][1] = s[mt][j][2] = s[mt][j][3] = 0.f;
     for (int kk = ks_begin; kk < ks_end; ++kk) {
-      uint32_t a[4];
-      ldsm_x4(a, qs + (uint32_t)((mi & 1) * 8 + l7) * row_bytes + (uint32_t)(kk * 16 + (mi >> 1) * 8) * 2);
+      uint32_t a[MT][4];
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+        ldsm_x4(a[mt], qs + (uint32_t)(mt * ROWS + (mi & 1) * 8 + l7) * row_bytes + (uint32_t)(kk * 16 + (mi >> 1) * 8) * 2);
 #pragma unroll
       for (int jp = 0; jp < 4; jp += 2) {
         uint32_t bq[4];
         ldsm_x4(bq, ks + (uint32_t)((jp + (mi >> 1)) * 8 + l7) * row_bytes + (uint32_t)(kk * 16 + (mi & 1) * 8) * 2);
-        mma16816(s[jp], a, bq[0], bq[1]);
-        mma16816(s[jp + 1], a, bq[2], bq[3]);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          mma16816(s[mt][jp], a[mt], bq[0], bq[1]);
+          mma16816(s[mt][jp + 1], a[mt], bq[2], bq[3]);
+        }
       }
     }
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
+    for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) sp[((warp * 4 + j) * 4 + e) * 32 + lane] = s[j][e];
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sp[(((warp * MT + mt) * 4 + j) * 4 + e) * 32 + lane] = s[mt][j][e];
     __syncthreads();
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
+    for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        float v = 0.f;
+      for (int j = 0; j < 4; ++j)
 #pragma unroll
-        for (int w = 0; w < WARPS; ++w) v += sp[((w * 4 + j) * 4 + e) * 32 + lane];  // warp order: reproducible
-        s[j][e] = v;
-      }
+        for (int e = 0; e < 4; ++e) {
+          float v = 0.f;
+#pragma unroll
+          for (int w = 0; w < WARPS; ++w) v += sp[(((w * MT + mt) * 4 + j) * 4 + e) * 32 + lane];  // warp order: reproducible
+          s[mt][j][e] = v;
+        }
     // ---- mask, running maximum, exponentials, running sum
     const int key0 = kv_lo + t * BN;
-    float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
+    for (int mt = 0; mt < MT; ++mt) {
+      float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int r = e >> 1;
-        const int kp = key0 + j * 8 + ((lane & 3) << 1) + (e & 1);
-        bool vis = (kp <= pos[r]) && (kp < kv_hi);
-        if (p.window > 0) vis = vis && (kp > pos[r] - p.window);
-        const float v = vis ? s[j][e] * p.scale_log2 : -INFINITY;
-        s[j][e] = v;
-        mx[r] = fmaxf(mx[r], v);
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int r = e >> 1;
+          const int kp = key0 + j * 8 + ((lane & 3) << 1) + (e & 1);
+          bool vis = (kp <= pos[mt][r]) && (kp < kv_hi);
+          if (p.window > 0) vis = vis && (kp > pos[mt][r] - p.window);
+          const float v = vis ? s[mt][j][e] * p.scale_log2 : -INFINITY;
+          s[mt][j][e] = v;
+          mx[r] = fmaxf(mx[r], v);
+        }
+      float corr[2], m_use[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        const float m_new = fmaxf(m[mt][r], mx[r]);
+        m_use[r] = (m_new == -INFINITY) ? 0.f : m_new;  // a row that has seen nothing yet
+        corr[r] = ex2(m[mt][r] - m_use[r]);
+        m[mt][r] = m_new;
       }
-    float corr[2], m_use[2];
+      float sum[2] = {0.f, 0.f};
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-      const float m_new = fmaxf(m[r], mx[r]);
-      m_use[r] = (m_new == -INFINITY) ? 0.f : m_new;  // a row that has seen nothing yet
-      corr[r] = ex2(m[r] - m_use[r]);
-      m[r] = m_new;
-    }
-    float sum[2] = {0.f, 0.f};
+      for (int j = 0; j < 4; ++j)
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
+        for (int e = 0; e < 4; ++e) {
+          const float pv = ex2(s[mt][j][e] - m_use[e >> 1]);
+          s[mt][j][e] = pv;
+          sum[e >> 1] += pv;
+        }
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float pv = ex2(s[j][e] - m_use[e >> 1]);
-        s[j][e] = pv;
-        sum[e >> 1] += pv;
+      for (int r = 0; r < 2; ++r) {
+        sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 1);
+        sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 2);
+        l[mt][r] = l[mt][r] * corr[r] + sum[r];
       }
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 1);
-      sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 2);
-      l[r] = l[r] * corr[r] + sum[r];
-    }
-#pragma unroll
-    for (int j = 0; j < NTW; ++j) {
-      o[j][0] *= corr[0];
-      o[j][1] *= corr[0];
-      o[j][2] *= corr[1];
-      o[j][3] *= corr[1];
+      for (int j = 0; j < NTW; ++j) {
+        o[mt][j][0] *= corr[0];
+        o[mt][j][1] *= corr[0];
+        o[mt][j][2] *= corr[1];
+        o[mt][j][3] *= corr[1];
+      }
     }
     // ---- O += P V over this warp's columns; the value tile is the key tile's first dv columns
     const int col0 = warp * NTW * 8;
 #pragma unroll
     for (int kk = 0; kk < BN / 16; ++kk) {
-      uint32_t a[4];
-      a[0] = pack2(s[2 * kk][0], s[2 * kk][1]);
-      a[1] = pack2(s[2 * kk][2], s[2 * kk][3]);
-      a[2] = pack2(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-      a[3] = pack2(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+      uint32_t a[MT][4];
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        a[mt][0] = pack2(s[mt][2 * kk][0], s[mt][2 * kk][1]);
+        a[mt][1] = pack2(s[mt][2 * kk][2], s[mt][2 * kk][3]);
+        a[mt][2] = pack2(s[mt][2 * kk + 1][0], s[mt][2 * kk + 1][1]);
+        a[mt][3] = pack2(s[mt][2 * kk + 1][2], s[mt][2 * kk + 1][3]);
+      }
 #pragma unroll
       for (int nt = 0; nt < NTW; nt += 2) {
         uint32_t bv[4];
         // four 8 x 8 blocks: (keys 0-7 | 8-15) x (columns n0.. | n0+8..), read transposed
         ldsm_x4_trans(bv, ks + (uint32_t)(kk * 16 + (mi & 1) * 8 + l7) * row_bytes + (uint32_t)(col0 + nt * 8 + (mi >> 1) * 8) * 2);
-        mma16816(o[nt], a, bv[0], bv[1]);
-        if (nt + 1 < NTW) mma16816(o[nt + 1], a, bv[2], bv[3]);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          mma16816(o[mt][nt], a[mt], bv[0], bv[1]);
+          if (nt + 1 < NTW) mma16816(o[mt][nt + 1], a[mt], bv[2], bv[3]);
+        }
       }
     }
     __syncthreads();  // the stage and the partial sums are free again
@@ -279,27 +311,30 @@ __global__ void __launch_bounds__(WARPS * 32) latent_attn_kernel(const LatParams
 
   // ---- write
 #pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    if (pos[h] < 0) continue;
-    const int r = (lane >> 2) + 8 * h;
-    const int tok = r / p.gh, head = chunk * p.gh + (r - tok * p.gh);
-    const int col = warp * NTW * 8 + ((lane & 3) << 1);
-    if (SPLIT) {
-      const size_t slot = ((size_t)b * p.nh + head) * p.max_splits + blockIdx.x;
-      if (warp == 0 && (lane & 3) == 0) {
-        p.part_ml[slot * 2] = m[h] * 0.69314718055994531f;  // natural-log units, as the merge reads them
-        p.part_ml[slot * 2 + 1] = l[h];
-      }
+  for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
-      for (int j = 0; j < NTW; ++j) {
-        p.part_acc[slot * p.dv + col + j * 8] = o[j][2 * h];
-        p.part_acc[slot * p.dv + col + j * 8 + 1] = o[j][2 * h + 1];
-      }
-    } else {
-      const float inv = l[h] > 0.f ? 1.f / l[h] : 0.f;
-      bf16* dst = p.out + (size_t)(q_begin + q0 + tok) * p.out_stride + (size_t)head * p.dv + col;
+    for (int h = 0; h < 2; ++h) {
+      if (pos[mt][h] < 0) continue;
+      const int r = mt * ROWS + (lane >> 2) + 8 * h;
+      const int tok = r / p.gh, head = chunk * p.gh + (r - tok * p.gh);
+      const int col = warp * NTW * 8 + ((lane & 3) << 1);
+      if (SPLIT) {
+        const size_t slot = ((size_t)b * p.nh + head) * p.max_splits + blockIdx.x;
+        if (warp == 0 && (lane & 3) == 0) {
+          p.part_ml[slot * 2] = m[mt][h] * 0.69314718055994531f;  // natural-log units, as the merge reads them
+          p.part_ml[slot * 2 + 1] = l[mt][h];
+        }
 #pragma unroll
-      for (int j = 0; j < NTW; ++j) *reinterpret_cast<uint32_t*>(dst + j * 8) = pack2(o[j][2 * h] * inv, o[j][2 * h + 1] * inv);
+        for (int j = 0; j < NTW; ++j) {
+          p.part_acc[slot * p.dv + col + j * 8] = o[mt][j][2 * h];
+          p.part_acc[slot * p.dv + col + j * 8 + 1] = o[mt][j][2 * h + 1];
+        }
+      } else {
+        const float inv = l[mt][h] > 0.f ? 1.f / l[mt][h] : 0.f;
+        bf16* dst = p.out + (size_t)(q_begin + q0 + tok) * p.out_stride + (size_t)head * p.dv + col;
+#pragma unroll
+        for (int j = 0; j < NTW; ++j) *reinterpret_cast<uint32_t*>(dst + j * 8) = pack2(o[mt][j][2 * h] * inv, o[mt][j][2 * h + 1] * inv);
+      }
     }
   }
 }
@@ -335,11 +370,22 @@ __global__ void latent_combine_kernel(const float* __restrict__ part_acc, const 
   }
 }
 
+template <int NTW, int MT>
+int launch_tiles(const LatParams& p, int B, int max_q_len, cudaStream_t st) {
+  const size_t smem = (size_t)(ROWS * MT + 2 * BN) * (p.d + PAD) * 2 + (size_t)WARPS * MT * 16 * 32 * sizeof(float);
+  auto kern = latent_attn_kernel<NTW, MT, false>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return launch(kern, dim3((max_q_len + p.tq - 1) / p.tq, B, p.chunks), dim3(WARPS * 32), smem, st, p);
+}
+
 template <int NTW>
-int launch_latent(const LatParams& p, int B, int max_q_len, int grid_splits, cudaStream_t st) {
+int launch_latent(LatParams p, int B, int max_q_len, int grid_splits, cudaStream_t st) {
   const size_t smem = (size_t)(ROWS + 2 * BN) * (p.d + PAD) * 2 + (size_t)WARPS * 16 * 32 * sizeof(float);
   if (p.split_size > 0) {
-    auto kern = latent_attn_kernel<NTW, true>;
+    auto kern = latent_attn_kernel<NTW, 1, true>;
     if (smem > 48 * 1024) {
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return (int)e;
@@ -349,12 +395,15 @@ int launch_latent(const LatParams& p, int B, int max_q_len, int grid_splits, cud
     return launch(latent_combine_kernel, dim3(p.nh, B), dim3(128), 0, st, (const float*)p.part_acc, (const float*)p.part_ml, p.out,
                   p.qsl, p.ctx_lens, p.nh, p.dv, p.out_stride, p.split_size, p.max_splits);
   }
-  auto kern = latent_attn_kernel<NTW, false>;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
+  // 32 rows a CTA where some sequence brings enough tokens to fill them
+  const int gh2 = p.nh < 2 * ROWS ? p.nh : 2 * ROWS;
+  if (max_q_len >= 2 * ROWS / gh2 && 2 * ROWS / gh2 >= 1 && max_q_len > p.tq) {
+    p.gh = gh2;
+    p.chunks = (p.nh + p.gh - 1) / p.gh;
+    p.tq = 2 * ROWS / p.gh;
+    return launch_tiles<NTW, 2>(p, B, max_q_len, st);
   }
-  return launch(kern, dim3((max_q_len + p.tq - 1) / p.tq, B, p.chunks), dim3(WARPS * 32), smem, st, p);
+  return launch_tiles<NTW, 1>(p, B, max_q_len, st);
 }
 
 }  // namespace
@@ -380,6 +429,9 @@ KVF_API int kvf_latent_attention_bf16(const void* q, void* out, const void* cach
   p.gh = nh < ROWS ? nh : ROWS;
   p.chunks = (nh + p.gh - 1) / p.gh;
   p.tq = ROWS / p.gh;
+  p.bs_shift = -1;
+  for (int sh = 0; sh < 31; ++sh)
+    if ((1 << sh) == block_size) p.bs_shift = sh;
   p.window = window; p.split_size = split_size; p.max_splits = max_splits;
   p.scale_log2 = scale * 1.4426950408889634f;
   if ((unsigned)B > 65535u || (unsigned)p.chunks > 65535u) return (int)cudaErrorInvalidValue;
