@@ -42,13 +42,11 @@ template <> __device__ __forceinline__ void load8<bf16>(const bf16* src, float* 
   bf16x8_to_float(*reinterpret_cast<const uint4*>(src), dst);
 }
 
-// One CTA of eight warps per RT tokens.  The warps share out the experts: a logit is one warp's dot product (a lane
+// One CTA of eight warps per RT tokens (one token a CTA while a step has few, four when it has many).  The warps share out the experts: a logit is one warp's dot product (a lane
 // adds its products in the order of the columns, then the lanes are summed in a fixed tree), so it does not depend on
 // the batch; a row of the router is read once for the CTA's tokens.  Then warp t chooses for token t.  Shared memory
 // per token: scores [E], choice scores [E], group scores [G], group flags [G].
-constexpr int RT = 4;
-
-template <typename T>
+template <typename T, int RT>
 __global__ void __launch_bounds__(256) moe_route_kernel(const T* __restrict__ x, long long x_stride,
                                                          const float* __restrict__ router, const float* __restrict__ correction,
                                                          int n_tokens, int W, int E, int top, int groups, int keep,
@@ -103,7 +101,7 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const T* __restrict__ x,
   float* gs = ch + E;
   float* ga = gs + groups;
   if (groups > 1 && keep < groups) {
-    // a group's score: the sum of its two largest choice scores; only the best `keep` groups stay
+    // a group is ranked by the sum of the top two shifted scores among its members; the `keep` best-ranked stay
     const int per = E / groups;
     for (int g = lane; g < groups; g += 32) {
       float a = -INFINITY, b = -INFINITY;
@@ -532,11 +530,15 @@ int run_products<bf16>(const bf16* x, long long x_stride, const bf16* w_up, cons
     if (E <= 0 || top <= 0 || top > E || groups <= 0 || E % groups || keep <= 0 || keep > groups ||                   \
         top > keep * (E / groups))                                                                                    \
       return (int)cudaErrorInvalidValue;                                                                              \
-    const size_t smem = (size_t)RT * (2 * E + 2 * groups) * sizeof(float);                                            \
+    const int rt = n_tokens <= 256 ? 1 : 4;                                                                           \
+    const size_t smem = (size_t)rt * (2 * E + 2 * groups) * sizeof(float);                                            \
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;                                                          \
     const int vec = (W % 8 == 0) && (x_stride % 8 == 0) && ((((uintptr_t)x) | ((uintptr_t)router)) % 16 == 0);        \
-    return launch(moe_route_kernel<T>, dim3((n_tokens + RT - 1) / RT), dim3(256), smem, st, (const T*)x, x_stride, router, \
-                  correction, n_tokens, W, E, top, groups, keep, norm_eps, vec, ids, wts);                            \
+    if (rt == 1)                                                                                                      \
+      return launch(moe_route_kernel<T, 1>, dim3(n_tokens), dim3(256), smem, st, (const T*)x, x_stride, router,       \
+                    correction, n_tokens, W, E, top, groups, keep, norm_eps, vec, ids, wts);                          \
+    return launch(moe_route_kernel<T, 4>, dim3((n_tokens + 3) / 4), dim3(256), smem, st, (const T*)x, x_stride,       \
+                  router, correction, n_tokens, W, E, top, groups, keep, norm_eps, vec, ids, wts);                    \
   }                                                                                                                   \
   KVF_API int kvf_moe_experts_##SUF(const void* x, long long x_stride, const void* w_up, const void* w_down,          \
                                     const int* ids, const float* wts, int n_tokens, int W, int ff, int E, int top,    \

@@ -1,6 +1,6 @@
 """The Setenex decoder as a ``ModelSpec``: which parts, with which constants, under which tensor
 names.  Every layer is the parallel arrangement (one norm; the mixer and the feed-forward both read
-its output and both add to the stream) with a norm whose weight is stored around zero; its mixer is
+its output and both add to the stream) with a norm whose tensor holds the weight's offset from one; its mixer is
 grouped-query attention without rotation whose heads are normed and whose scores take a bias by
 distance, under a window that keeps the first tokens (``attention``), or attention over a latent shared
 by keys and values with a gate per head (``latent_attention``); its feed-forward, where it has one, is

@@ -1488,7 +1488,7 @@ def moe_route(
 ) -> None:  # fmt: skip
     """Per token of ``x [N, W]``: logits ``router [E, W] x`` in float, scores ``s = sigmoid(z)``; the ``top``
     experts with the largest ``s + correction`` among the best ``keep`` of ``groups`` equal groups of
-    neighbouring experts (a group's score: the sum of its two largest ``s + correction``) are chosen
+    neighbouring experts (a group's rank: the sum of the top two ``s + correction`` among its members) are chosen
     (``ids`` int32 ``[N, top]``); their weights are their ``s`` over the sum of those (+ ``norm_eps``)
     (``weights`` float ``[N, top]``)."""
     s = _suffix(x.dtype)

@@ -21,8 +21,8 @@ WEIGHT_SUM_EPS = 1e-20  # added to the sum of the chosen scores before the divis
 class RoutedExperts(FeedForward):
     """params: ``hidden_size``, ``experts``, ``top``, ``intermediate_size`` (of one expert), ``activation``
     (only ``"gelu"``, the exact one); optional ``groups`` and ``keep`` (the experts form ``groups`` equal
-    groups of neighbours; a group's score is the sum of its two largest choice scores and only experts
-    of the best ``keep`` groups can be chosen) and ``correction`` (default true: the tensor
+    groups of neighbours; a group is ranked by the sum of the top two shifted scores among its members, and
+    only members of the ``keep`` best-ranked groups are eligible) and ``correction`` (default true: the tensor
     ``correction [experts]`` is added to the scores for the choice).
 
     Tensors: ``router [E, W]``, ``correction [E]``, ``e<i>.up [ff, W]``, ``e<i>.down [W, ff]``."""

@@ -33,7 +33,7 @@ class LatentAttention(Mixer):
     interleaved pairs over at most ``rot_dim`` dims, or ``None``) and ``gate`` (``"sigmoid"``: every head's
     result is multiplied by the logistic function of one more projection of the input, or ``None``).
 
-    Tensors: ``q [H*(head_dim+rot_dim), W]`` (head by head, the part that does not turn first),
+    Tensors: ``q [H*(head_dim+rot_dim), W]`` (one head after the other, in each the part that does not turn first),
     ``dkv [kv_rank+rot_dim, W]``, ``dkv.norm [kv_rank]``, ``uk [H*head_dim, kv_rank]``,
     ``uv [H*v_head_dim, kv_rank]``, ``g [H, W]`` (with a gate), ``o [W, H*v_head_dim]``."""
 
@@ -113,7 +113,7 @@ class LatentAttention(Mixer):
     def _per_head(self, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
         """``out[:, h] = a[:, h] @ W[h]`` for every head: ``a [N, H, K]`` and ``out [N, H, M]`` are views
         whose rows may be wider than they are.  bfloat16: one batched library product; 32-bit: the
-        engine's own product, head by head."""
+        engine's own product, one launch a head."""
         if a.dtype == torch.float32:
             for h in range(self.nh):
                 ops.gemm_nt_f32(a[:, h], w[h], out[:, h])

@@ -15,7 +15,7 @@ from .base import Norm, WeightDecl, register_norm
 
 @register_norm("rmsnorm")
 class RMSNorm(Norm):
-    """params: ``dim``, ``eps``; optional ``one_plus`` (the tensor is stored around zero and the rows
+    """params: ``dim``, ``eps``; optional ``one_plus`` (the tensor holds the weight's offset from one and the rows
     are multiplied by ``1 + w``; the sum is made once, in 32-bit, when the tensor is bound)."""
 
     def __init__(self, params, prefix=""):

@@ -41,7 +41,7 @@ def draw(name: str, decl: WeightDecl, seed: int, device: torch.device | str = "c
         if norm_std:
             t += norm_std * torch.randn(decl.shape, generator=g, dtype=torch.float32, device=device)
         return t
-    if decl.init == "zeros":  # a weight stored around zero (a norm that multiplies by one plus it, a bias)
+    if decl.init == "zeros":  # a weight kept as an offset (a norm that multiplies by one plus it, a bias)
         return (norm_std or init_std) * torch.randn(decl.shape, generator=g, dtype=torch.float32, device=device)
     if decl.init == "eye":  # a mixing matrix near the identity
         t = torch.eye(decl.shape[0], decl.shape[1], dtype=torch.float32, device=device)

@@ -48,7 +48,7 @@ def rms(x: torch.Tensor, eps: float) -> torch.Tensor:
 
 
 def norm_one_plus(x, w, eps):
-    """The layers' and the model's norm: the weight is stored around zero."""
+    """The layers' and the model's norm: the tensor holds the weight's offset from one."""
     return rms(x, eps) * (1.0 + w)
 
 
@@ -70,7 +70,7 @@ def distance_bucket(n: int, rows: int, far: int) -> int:
 
 
 def rotate_pairs(x, positions, dims: int, base: float):
-    """``x [T, ..., d]``: dims (2i, 2i+1), i < dims/2, turn by ``p * base^(-2i/dims)``; the rest pass."""
+    """``x [T, ..., d]``: dims (2i, 2i+1), i < dims/2, turn by ``p * base^(-2i/dims)``; the other dims are left as they are."""
     freqs = torch.tensor([base ** (-2.0 * i / dims) for i in range(dims // 2)], dtype=torch.float64)
     ang = positions.to(torch.float64)[:, None] * freqs[None, :]
     shape = [x.shape[0]] + [1] * (x.dim() - 2) + [dims // 2]

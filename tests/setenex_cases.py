@@ -139,7 +139,7 @@ def random_tensors(config: dict, seed: int, fixed_choice: bool = False) -> dict[
         if name == "embed":
             t = r
         elif leaf in ("norm1",) or name == "final.norm":
-            t = 0.2 * r  # stored around zero
+            t = 0.2 * r  # an offset from one
         elif leaf == "norm":
             t = 1.0 + 0.2 * r
         elif leaf == "rel":

@@ -240,7 +240,7 @@ def step_mixer(part, rt, x, cache_k, cache_v, bs, table, cuts, group_cache):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("window,keep", [(None, 0), (7, 0), (7, 3), (5, 9), (70, 66)])
-@pytest.mark.parametrize("dk,dv,t", [(24, 16, 45), (64, 64, 200)])
+@pytest.mark.parametrize("dk,dv,t", [(24, 16, 45), (64, 64, 200), (128, 128, 150)])
 def test_attention_with_normed_heads_bias_and_kept_tokens(dtype, window, keep, dk, dv, t):
     """The whole sequence in one step, then portions and single tokens on top of the cache (the decode
     form: key ranges in parallel), against the plain mixer.  Heads of 64 in bfloat16 go to the tensor-core

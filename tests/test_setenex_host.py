@@ -80,7 +80,7 @@ def test_a_window_group_keeps_the_pages_of_the_first_tokens():
 
 
 def test_plain_route_groups_and_weights():
-    """The plain router on a hand-made case: the best groups by their two largest choice scores, the
+    """The plain router on a hand-made case: groups ranked by the sum of their top two shifted scores, the
     choice with the correction, the weights without it."""
     w = {"m.router": torch.eye(8, dtype=torch.float64), "m.correction": torch.tensor([0.0, 0, 0, 0, 0, 0, 0.9, 0], dtype=torch.float64)}
     z = torch.tensor([[2.0, 1.9, -9, -9, 3.0, -9, -1.0, -9]], dtype=torch.float64)
