@@ -11,6 +11,8 @@ first layer, in the middle, to the last layer, and none.
 
 from __future__ import annotations
 
+import random
+
 import torch
 
 import plain_setenex as plain
@@ -159,3 +161,44 @@ def random_tensors(config: dict, seed: int, fixed_choice: bool = False) -> dict[
 def plain_logits(config: dict, tensors: dict[str, torch.Tensor], tokens: list[int]) -> torch.Tensor:
     w = {k: v.double() for k, v in tensors.items()}
     return plain.logits(config, w, tokens)
+
+
+def random_config(seed: int) -> dict:
+    """A configuration drawn at random: widths that are and are not multiples of 8, one to twenty heads, one key head
+    or several, key and value sizes from 8 to 128, tables of 2 to 40 rows, windows of 1 to 100 tokens or none, up to 40
+    kept tokens, latents of 8 to 160 numbers, 4 to 24 experts in any grouping that divides them, layers without a
+    feed-forward, a loop over any stretch (or none) with one to three passes."""
+    rng = random.Random(seed)
+    m8 = lambda lo, hi: 8 * rng.randint(lo, hi)  # noqa: E731
+    width = rng.choice([m8(5, 24), 100, 132])
+    n_layers = rng.randint(2, 5)
+    experts = rng.choice([4, 6, 9, 10, 16, 24])
+    divisors = [g for g in range(1, experts + 1) if experts % g == 0]
+    layers = []
+    for _ in range(n_layers):
+        if rng.random() < 0.5:
+            kv = rng.choice([1, 2, 3])
+            heads = kv * rng.choice([1, 2, 3, 5])
+            dim = rng.choice([8, 16, 24, 40, 64, 128])
+            vdim = dim if rng.random() < 0.5 else rng.choice([8, 16, 48, 72])
+            rows = rng.randint(2, 40)
+            far = rng.randint(rows // 2 + 1, 300)
+            window = rng.choice([None, rng.randint(1, 90)])
+            keep = rng.randint(0, 40) if window else 0
+            kind, mixer = "attention", attention(heads, kv, dim, vdim, rows, far, window, keep, scale=rng.uniform(0.05, 0.3))
+        else:
+            heads, dim, rot = rng.choice([1, 2, 5, 8, 16, 20]), rng.choice([8, 16, 32]), rng.choice([8, 16, 32, 64])
+            rank, vdim = rng.choice([8, 24, 32, 48, 64, 96, 128, 160]), rng.choice([8, 24, 40])
+            window = rng.choice([None, rng.randint(1, 100)])
+            kind, mixer = "latent_attention", latent(heads, dim, rot, vdim, rank, window, base=rng.choice([100.0, 10000.0, 1e6]), scale=rng.uniform(0.05, 0.3))
+        groups = rng.choice(divisors)
+        keep_groups = rng.randint(1, groups)
+        top = rng.randint(1, min(keep_groups * (experts // groups), 6))
+        mlp = None if rng.random() < 0.2 else moe(experts, top, m8(2, 12), groups, keep_groups)
+        layers.append(layer(kind, mixer, mlp))
+    config = {"architecture": "Setenex", "vocab": rng.randint(30, 300), "width": width, "norm": {"eps": rng.choice([1e-5, 1e-6])},
+              "embedding": {"scale": rng.uniform(0.5, 12)}, "layers": layers}  # fmt: skip
+    if rng.random() < 0.7:
+        start = rng.randint(0, n_layers - 1)
+        config["loop"] = {"start": start, "stop": rng.randint(start + 1, n_layers), "times": rng.randint(1, 3)}
+    return config

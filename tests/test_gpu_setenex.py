@@ -16,7 +16,7 @@ import torch
 
 import plain_setenex as plain
 import traces
-from setenex_cases import CASES, attention, latent, plain_logits, random_tensors, row_error, write_folder
+from setenex_cases import CASES, attention, latent, plain_logits, random_config, random_tensors, row_error, write_folder
 from test_gpu_mopilorn import check, run_trace, tokens
 from test_gpu_parts import context, runtime
 
@@ -105,6 +105,21 @@ def test_batch_and_cutting_change_float32_logits_by_rounding_only(models):
         for i, place in enumerate(rows):
             worst = max(worst, float((got[i] - by_place[place]).abs().max()))
     assert worst <= 2e-5 * scale, worst
+
+
+@pytest.mark.parametrize("seed", [3, 12, 29, 41, 57, 68])
+def test_configurations_drawn_at_random(tmp_path, seed):
+    """Sizes that no hand-made case has (widths and inner sizes that are no multiple of 8 or of 16, one head, twenty
+    heads, one expert a token out of ungrouped experts, a single pass of a loop, ...), each replayed whole, in
+    portions and mixed, in both storage types."""
+    config = random_config(seed)
+    block_size = [4, 8, 16, 32][seed % 4]
+    for dtype, fixed in (("float32", False), ("bfloat16", True)):
+        folder, reqs, ref, scale, _ = build(tmp_path, f"drawn-{dtype}", config, random_tensors(config, 100 + seed, fixed_choice=fixed), [90, 1, 37, 140], seed=seed)
+        for regime in ("whole", "portions", "mixed"):
+            steps = regime_steps(reqs, regime) if regime != "mixed" else traces.mixed(reqs, {r: max(1, len(t) - 10) for r, t in reqs.items()}, max_live=4, seed=seed)
+            outs, _ = run_trace(folder, dtype, steps, block_size)
+            check(steps, outs, ref, scale, TOL[dtype])
 
 
 def sharpened(w):
