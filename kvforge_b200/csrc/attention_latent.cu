@@ -5,12 +5,13 @@
 // has ctx_b rows after this step's writes and q_b queries; query i sits at p = ctx_b - q_b + i and sees
 // row j iff j <= p (and j > p - window when window > 0); scores and softmax in float, one rounding.
 //
-// A CTA of four warps owns 16 or 32 rows of (query token, head): all 16 heads of one or two tokens, or
-// several tokens of fewer heads, so that a tile of keys brought into shared memory serves every head
-// (32 rows where a step brings enough tokens: a tile is then fetched, and the warps meet, half as often).  Keys come
+// A CTA owns 16 or 32 rows of (query token, head), four warps per 16 rows: all 16 heads of one or two
+// tokens, or several tokens of fewer heads, so that a tile of keys brought into shared memory serves every
+// head (32 or 64 rows with eight or sixteen warps where a step brings enough tokens: a tile is then fetched less
+// often, and one group of four warps computes while another waits).  Keys come
 // in tiles of 32 that start at multiples of 32 (cp.async, two stages, rows padded by 16 bytes so that
 // the 8 rows of an ldmatrix lie in different banks).  Per tile:
-//   scores   the four warps share out the k-steps of q . k (d/16 of them), leave their partial
+//   scores   the four warps of 16 rows share out the k-steps of q . k (d/16 of them), leave their partial
 //            [16 x 32] sums in shared memory and add the four in warp order;
 //   softmax  every warp for itself (the same numbers in all four);
 //   values   every warp owns dv/4 output columns: O[16 x dv/4] += P[16 x 32] V[32 x dv/4], the value
@@ -78,9 +79,11 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
-// NTW: n-tiles of 8 output columns per warp (dv = 32 * NTW).  MT: m-tiles of 16 rows per CTA.
+// NTW: n-tiles of 8 output columns per warp (dv = 32 * NTW).  MT: m-tiles of 16 rows per CTA, each with four warps
+// of its own (`group` is a warp's m-tile, `w4` its place among the four).
 template <int NTW, int MT, bool SPLIT>
-__global__ void __launch_bounds__(WARPS * 32) latent_attn_kernel(const LatParams p) {
+__global__ void __launch_bounds__(WARPS * 32 * MT) latent_attn_kernel(const LatParams p) {
+  constexpr int ML = 1;  // m-tiles a warp holds
   pdl_launch();
   pdl_wait();
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -90,12 +93,13 @@ __global__ void __launch_bounds__(WARPS * 32) latent_attn_kernel(const LatParams
   const uint32_t qs = su32(smem_raw);                       // [RWS][ld]
   const uint32_t ks0 = qs + RWS * row_bytes;                // [2][BN][ld]
   const uint32_t k_stage = BN * row_bytes;
-  float* sp = reinterpret_cast<float*>(smem_raw + (size_t)(RWS + 2 * BN) * row_bytes);  // [WARPS][MT][4][4][32]
+  float* sp = reinterpret_cast<float*>(smem_raw + (size_t)(RWS + 2 * BN) * row_bytes);  // [MT][WARPS][4][4][32]
 
   const int b = blockIdx.y, chunk = blockIdx.z;
   const int q_begin = p.qsl[b], q_len = p.qsl[b + 1] - q_begin;
   const int ctx = p.ctx_lens[b];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int group = warp >> 2, w4 = warp & 3;
   if (q_len <= 0 || ctx <= 0) return;
 
   int q0, n_tok, p_first, kv_lo, kv_hi;
@@ -145,8 +149,8 @@ __global__ void __launch_bounds__(WARPS * 32) latent_attn_kernel(const LatParams
   auto load_tile = [&](int stage, int t0) {
     const uint32_t dst0 = ks0 + stage * k_stage;
 #pragma unroll 2
-    for (int i = 0; i < BN / WARPS; ++i) {
-      const int key = warp * (BN / WARPS) + i;
+    for (int i = 0; i < BN / (WARPS * MT); ++i) {
+      const int key = warp * (BN / (WARPS * MT)) + i;
       const int kp = t0 + key;
       const int page = p.bs_shift >= 0 ? kp >> p.bs_shift : kp / p.block_size;
       const int off = p.bs_shift >= 0 ? kp & (p.block_size - 1) : kp - page * p.block_size;
@@ -159,13 +163,13 @@ __global__ void __launch_bounds__(WARPS * 32) latent_attn_kernel(const LatParams
   };
 
   // the two rows of every m-tile that a thread holds: lane/4 and lane/4 + 8
-  int pos[MT][2];
-  float o[MT][NTW][4], m[MT][2], l[MT][2];
+  int pos[ML][2];
+  float o[ML][NTW][4], m[ML][2], l[ML][2];
 #pragma unroll
-  for (int mt = 0; mt < MT; ++mt) {
+  for (int mt = 0; mt < ML; ++mt) {
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-      const int r = mt * ROWS + (lane >> 2) + 8 * h;
+      const int r = (group + mt) * ROWS + (lane >> 2) + 8 * h;
       const int tok = r / p.gh, hh = chunk * p.gh + (r - tok * p.gh);
       pos[mt][h] = (tok < n_tok && hh < p.nh) ? p_first + tok : -1;  // -1: sees nothing
       m[mt][h] = -INFINITY;
@@ -176,7 +180,7 @@ __global__ void __launch_bounds__(WARPS * 32) latent_attn_kernel(const LatParams
   }
 
   const int n_ksteps = d / 16;
-  const int ks_begin = (warp * n_ksteps) / WARPS, ks_end = ((warp + 1) * n_ksteps) / WARPS;
+  const int ks_begin = (w4 * n_ksteps) / WARPS, ks_end = ((w4 + 1) * n_ksteps) / WARPS;
   const int mi = lane >> 3, l7 = lane & 7;
   const int n_tiles = (kv_hi - kv_lo + BN - 1) / BN;
   load_tile(0, kv_lo);
@@ -193,49 +197,49 @@ __global__ void __launch_bounds__(WARPS * 32) latent_attn_kernel(const LatParams
     __syncthreads();  // the tile (and, the first time, the query rows) are in shared memory
     const uint32_t ks = ks0 + st * k_stage;
     // ---- this warp's share of the k-steps of q . k
-    float s[MT][4][4];
+    float s[ML][4][4];
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
+    for (int mt = 0; mt < ML; ++mt)
 #pragma unroll
       for (int j = 0; j < 4; ++j) s[mt][j][0] = s[mt][j][1] = s[mt][j][2] = s[mt][j][3] = 0.f;
     for (int kk = ks_begin; kk < ks_end; ++kk) {
-      uint32_t a[MT][4];
+      uint32_t a[ML][4];
 #pragma unroll
-      for (int mt = 0; mt < MT; ++mt)
-        ldsm_x4(a[mt], qs + (uint32_t)(mt * ROWS + (mi & 1) * 8 + l7) * row_bytes + (uint32_t)(kk * 16 + (mi >> 1) * 8) * 2);
+      for (int mt = 0; mt < ML; ++mt)
+        ldsm_x4(a[mt], qs + (uint32_t)((group + mt) * ROWS + (mi & 1) * 8 + l7) * row_bytes + (uint32_t)(kk * 16 + (mi >> 1) * 8) * 2);
 #pragma unroll
       for (int jp = 0; jp < 4; jp += 2) {
         uint32_t bq[4];
         ldsm_x4(bq, ks + (uint32_t)((jp + (mi >> 1)) * 8 + l7) * row_bytes + (uint32_t)(kk * 16 + (mi & 1) * 8) * 2);
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
+        for (int mt = 0; mt < ML; ++mt) {
           mma16816(s[mt][jp], a[mt], bq[0], bq[1]);
           mma16816(s[mt][jp + 1], a[mt], bq[2], bq[3]);
         }
       }
     }
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
+    for (int mt = 0; mt < ML; ++mt)
 #pragma unroll
       for (int j = 0; j < 4; ++j)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) sp[(((warp * MT + mt) * 4 + j) * 4 + e) * 32 + lane] = s[mt][j][e];
+        for (int e = 0; e < 4; ++e) sp[((((group + mt) * WARPS + w4) * 4 + j) * 4 + e) * 32 + lane] = s[mt][j][e];
     __syncthreads();
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
+    for (int mt = 0; mt < ML; ++mt)
 #pragma unroll
       for (int j = 0; j < 4; ++j)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           float v = 0.f;
 #pragma unroll
-          for (int w = 0; w < WARPS; ++w) v += sp[(((w * MT + mt) * 4 + j) * 4 + e) * 32 + lane];  // warp order: reproducible
+          for (int w = 0; w < WARPS; ++w) v += sp[((((group + mt) * WARPS + w) * 4 + j) * 4 + e) * 32 + lane];  // warp order: reproducible
           s[mt][j][e] = v;
         }
     // ---- mask, running maximum, exponentials, running sum
     const int key0 = kv_lo + t * BN;
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
+    for (int mt = 0; mt < ML; ++mt) {
       float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
       for (int j = 0; j < 4; ++j)
@@ -283,12 +287,12 @@ __global__ void __launch_bounds__(WARPS * 32) latent_attn_kernel(const LatParams
       }
     }
     // ---- O += P V over this warp's columns; the value tile is the key tile's first dv columns
-    const int col0 = warp * NTW * 8;
+    const int col0 = w4 * NTW * 8;
 #pragma unroll
     for (int kk = 0; kk < BN / 16; ++kk) {
-      uint32_t a[MT][4];
+      uint32_t a[ML][4];
 #pragma unroll
-      for (int mt = 0; mt < MT; ++mt) {
+      for (int mt = 0; mt < ML; ++mt) {
         a[mt][0] = pack2(s[mt][2 * kk][0], s[mt][2 * kk][1]);
         a[mt][1] = pack2(s[mt][2 * kk][2], s[mt][2 * kk][3]);
         a[mt][2] = pack2(s[mt][2 * kk + 1][0], s[mt][2 * kk + 1][1]);
@@ -300,7 +304,7 @@ __global__ void __launch_bounds__(WARPS * 32) latent_attn_kernel(const LatParams
         // four 8 x 8 blocks: (keys 0-7 | 8-15) x (columns n0.. | n0+8..), read transposed
         ldsm_x4_trans(bv, ks + (uint32_t)(kk * 16 + (mi & 1) * 8 + l7) * row_bytes + (uint32_t)(col0 + nt * 8 + (mi >> 1) * 8) * 2);
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
+        for (int mt = 0; mt < ML; ++mt) {
           mma16816(o[mt][nt], a[mt], bv[0], bv[1]);
           if (nt + 1 < NTW) mma16816(o[mt][nt + 1], a[mt], bv[2], bv[3]);
         }
@@ -311,16 +315,16 @@ __global__ void __launch_bounds__(WARPS * 32) latent_attn_kernel(const LatParams
 
   // ---- write
 #pragma unroll
-  for (int mt = 0; mt < MT; ++mt) {
+  for (int mt = 0; mt < ML; ++mt) {
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       if (pos[mt][h] < 0) continue;
-      const int r = mt * ROWS + (lane >> 2) + 8 * h;
+      const int r = (group + mt) * ROWS + (lane >> 2) + 8 * h;
       const int tok = r / p.gh, head = chunk * p.gh + (r - tok * p.gh);
-      const int col = warp * NTW * 8 + ((lane & 3) << 1);
+      const int col = w4 * NTW * 8 + ((lane & 3) << 1);
       if (SPLIT) {
         const size_t slot = ((size_t)b * p.nh + head) * p.max_splits + blockIdx.x;
-        if (warp == 0 && (lane & 3) == 0) {
+        if (w4 == 0 && (lane & 3) == 0) {
           p.part_ml[slot * 2] = m[mt][h] * 0.69314718055994531f;  // natural-log units, as the merge reads them
           p.part_ml[slot * 2 + 1] = l[mt][h];
         }
@@ -378,7 +382,7 @@ int launch_tiles(const LatParams& p, int B, int max_q_len, cudaStream_t st) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  return launch(kern, dim3((max_q_len + p.tq - 1) / p.tq, B, p.chunks), dim3(WARPS * 32), smem, st, p);
+  return launch(kern, dim3((max_q_len + p.tq - 1) / p.tq, B, p.chunks), dim3(WARPS * 32 * MT), smem, st, p);
 }
 
 template <int NTW>
@@ -395,13 +399,17 @@ int launch_latent(LatParams p, int B, int max_q_len, int grid_splits, cudaStream
     return launch(latent_combine_kernel, dim3(p.nh, B), dim3(128), 0, st, (const float*)p.part_acc, (const float*)p.part_ml, p.out,
                   p.qsl, p.ctx_lens, p.nh, p.dv, p.out_stride, p.split_size, p.max_splits);
   }
-  // 32 rows a CTA where some sequence brings enough tokens to fill them
-  const int gh2 = p.nh < 2 * ROWS ? p.nh : 2 * ROWS;
-  if (max_q_len >= 2 * ROWS / gh2 && 2 * ROWS / gh2 >= 1 && max_q_len > p.tq) {
-    p.gh = gh2;
-    p.chunks = (p.nh + p.gh - 1) / p.gh;
-    p.tq = 2 * ROWS / p.gh;
-    return launch_tiles<NTW, 2>(p, B, max_q_len, st);
+  // 64 or 32 rows a CTA (16 or 8 warps) where some sequence brings enough tokens to fill them
+  for (int mt = 4; mt >= 2; mt >>= 1) {
+    const int rows = mt * ROWS;
+    const int gh = p.nh < rows ? p.nh : rows;
+    const int tq = rows / gh;
+    if (tq < 1 || max_q_len < tq || tq <= p.tq) continue;
+    if ((size_t)(rows + 2 * BN) * (p.d + PAD) * 2 + (size_t)WARPS * mt * 16 * 32 * sizeof(float) > 220 * 1024) continue;
+    p.gh = gh;
+    p.chunks = (p.nh + gh - 1) / gh;
+    p.tq = tq;
+    return mt == 4 ? launch_tiles<NTW, 4>(p, B, max_q_len, st) : launch_tiles<NTW, 2>(p, B, max_q_len, st);
   }
   return launch_tiles<NTW, 1>(p, B, max_q_len, st);
 }
