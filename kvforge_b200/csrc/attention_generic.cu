@@ -8,8 +8,8 @@
 // query i sits at position p = ctx_b - q_b + i and sees key j iff j <= p (and
 // j > p - window when window > 0, or j < keep_first: the first keys of a sequence may stay
 // visible at any distance).  S = scale * (q . k) in float, plus, when a table is given, a learned
-// bias by distance: bias[bucket[min(p - j, far)]][head], with `bucket` an int table of far + 1
-// entries and `bias` float [rows][nh]; softmax in float, O = P V in float, one rounding to T.
+// bias by distance: bias[head][min(p - j, far)], `bias` float [nh][far + 1] (a head's values for
+// neighbouring keys lie side by side); softmax in float, O = P V in float, one rounding to T.
 //
 // Exactness: keys are walked in tiles of 32 that start at absolute positions (multiples
 // of 32), each score is one thread's sequential dot product, and a fully masked tile
@@ -46,8 +46,7 @@ struct AttnParams {
   int gh, chunks, tq;  // heads per CTA, head chunks per kv head, tokens per CTA
   int window, keep_first;
   int v_stride;           // elements between the value rows of neighbouring keys in a page
-  const float* bias;      // [rows][nh] or null
-  const int* bias_bucket; // [bias_far + 1]: row of `bias` for a distance
+  const float* bias;      // [nh][bias_far + 1] or null
   int bias_far;
   int split_size, max_splits;
   float scale;
@@ -210,7 +209,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attn_generic_kernel(const At
       float sc = -INFINITY;
       if (vis) {
         sc = s[i] * p.scale;
-        if (p.bias) sc += __ldg(p.bias + (size_t)__ldg(p.bias_bucket + min(pos[i] - kp, p.bias_far)) * p.nh + hd[i]);
+        if (p.bias) sc += __ldg(p.bias + (size_t)hd[i] * (p.bias_far + 1) + min(pos[i] - kp, p.bias_far));
       }
       const float tmax = warp_max(sc);
       const float m_new = fmaxf(m[i], tmax);
@@ -335,14 +334,14 @@ int paged_attention_generic(const void* q, void* out, const void* kcache, const 
                             int max_q_len, int q_stride, int out_stride, int bt_stride, int nh, int nkv,
                             int d, int dv, int block_size, float scale, int window, int split_size, int max_splits,
                             int grid_splits, float* part_acc, float* part_ml, int keep_first, int v_stride,
-                            const float* bias, const int* bias_bucket, int bias_far, cudaStream_t st) {
+                            const float* bias, int bias_far, cudaStream_t st) {
   if (B <= 0 || max_q_len <= 0) return 0;
   if (dv <= 0) dv = d;
   if (v_stride <= 0) v_stride = dv;
   if (d <= 0 || d > 1024 || (d % 8) != 0 || dv > 512 || (dv % 8) != 0 || nkv <= 0 || nh % nkv != 0 || block_size <= 0)
     return (int)cudaErrorInvalidValue;
   if (vcache == kcache && (v_stride != d || dv > d)) return (int)cudaErrorInvalidValue;
-  if (bias && (!bias_bucket || bias_far < 0)) return (int)cudaErrorInvalidValue;
+  if (bias && bias_far < 0) return (int)cudaErrorInvalidValue;
   if (keep_first < 0) return (int)cudaErrorInvalidValue;
   AttnParams p;
   p.q = q; p.out = out; p.kcache = kcache; p.vcache = vcache;
@@ -356,7 +355,7 @@ int paged_attention_generic(const void* q, void* out, const void* kcache, const 
   p.tq = ROWS / p.gh;
   p.window = window; p.scale = scale;
   p.keep_first = window > 0 ? keep_first : 0; p.v_stride = v_stride;
-  p.bias = bias; p.bias_bucket = bias_bucket; p.bias_far = bias_far;
+  p.bias = bias; p.bias_far = bias_far;
   p.split_size = split_size; p.max_splits = max_splits;
   if ((unsigned)B > 65535u || (unsigned)(nkv * p.chunks) > 65535u) return (int)cudaErrorInvalidValue;
   if (split_size > 0) {
@@ -383,11 +382,11 @@ int paged_attention_generic(const void* q, void* out, const void* kcache, const 
       const int* qsl, const int* ctx_lens, int B, int max_q_len, int q_stride, int out_stride,            \
       int bt_stride, int nh, int nkv, int d, int dv, int block_size, float scale, int window,             \
       int split_size, int max_splits, int grid_splits, float* part_acc, float* part_ml, int keep_first,   \
-      int v_stride, const float* bias, const int* bias_bucket, int bias_far, cudaStream_t st) {           \
+      int v_stride, const float* bias, int bias_far, cudaStream_t st) {                                   \
     return paged_attention_generic<T>(q, out, kcache, vcache, block_tables, qsl, ctx_lens, B, max_q_len,  \
                                       q_stride, out_stride, bt_stride, nh, nkv, d, dv, block_size, scale, \
                                       window, split_size, max_splits, grid_splits, part_acc, part_ml,     \
-                                      keep_first, v_stride, bias, bias_bucket, bias_far, st);             \
+                                      keep_first, v_stride, bias, bias_far, st);                          \
   }
 
 KVF_ATTN_API(f32, float)

@@ -3,7 +3,7 @@
 // this step's writes and q_b queries; query i sits at p = ctx_b - q_b + i and sees key j
 // iff j <= p (and j > p - window when window > 0); softmax in float, one rounding.  The tile
 // Both forms also take, under a window, first keys that stay visible at any distance (j < keep_first)
-// and a bias on the scaled scores by distance and head: bias[bucket[min(p - j, far)]][head].
+// and a bias on the scaled scores by distance and head: bias[head][min(p - j, far)] (float [nh][far + 1]).
 //
 // One CTA serves one kv head of one sequence.  The MMA's 16 rows are (query token, head of
 // the group) pairs, so the g query heads that share a kv head share every K/V tile that is
@@ -49,8 +49,7 @@ struct MmaParams {
   float scale_log2;  // scale * log2(e)
   // first keys that every later query sees, and the bias by distance (null: none)
   int keep_first;
-  const float* bias;       // [rows][nh]
-  const int* bias_bucket;  // [bias_far + 1]
+  const float* bias;       // [nh][bias_far + 1]
   int bias_far;
 };
 
@@ -175,16 +174,33 @@ __device__ __forceinline__ void pv_tile(float (&o)[D / 8][4], const float (&s)[2
 // (lane/4 and lane/4 + 8) over NT n-tiles whose first key is `key0`.  Row r sees keys
 // lo[r] <= k <= hi[r].  Scores come in as raw dot products and leave as probabilities
 // relative to the new maximum.
-// EXTRA: keys below `keep_first` are seen whatever lo says, and bias[bucket[min(qpos[r] - k, far)] * nh + head[r]]
+// EXTRA: keys below `keep_first` are seen whatever lo says, and bias[head[r] * (far + 1) + min(qpos[r] - k, far)]
 // is added to the scaled score (qpos[r] is the row's own position).
 template <int NT, int ND, bool EXTRA = false>
 __device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&o)[ND][4], float (&m)[2], float (&l)[2],
                                              const int (&lo)[2], const int (&hi)[2], int key0, float scale_log2,
                                              int lane, bool need_mask, int keep_first = 0, const float* bias = nullptr,
-                                             const int* bucket = nullptr, int far = 0, int nh = 0, const int* head = nullptr,
+                                             int far = 0, const int* head = nullptr,
                                              const int* qpos = nullptr) {
   float mx[2] = {-INFINITY, -INFINITY};
-  if (EXTRA) {
+  // a tile that every row sees whole, with every distance inside the table: no masks, no clamps, and a row's
+  // biases for neighbouring keys are neighbouring words below one pointer
+  bool fast = EXTRA && !need_mask;
+  if (EXTRA && fast && bias) fast = !__any_sync(0xffffffffu, (qpos[0] - key0 > far) || (qpos[1] - key0 > far));
+  if (EXTRA && fast) {
+    const float* b0 = bias ? bias + (size_t)head[0] * (far + 1) + (qpos[0] - key0 - ((lane & 3) << 1)) : nullptr;
+    const float* b1 = bias ? bias + (size_t)head[1] * (far + 1) + (qpos[1] - key0 - ((lane & 3) << 1)) : nullptr;
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float v = s[j][e] * scale_log2;
+        if (bias) v = fmaf(__ldg(((e >> 1) ? b1 : b0) - (j * 8 + (e & 1))), 1.4426950408889634f, v);
+        s[j][e] = v;
+        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+      }
+    }
+  } else if (EXTRA) {
 #pragma unroll
     for (int j = 0; j < NT; ++j) {
 #pragma unroll
@@ -195,7 +211,7 @@ __device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&o)[ND][4
         float v = -INFINITY;
         if (vis) {
           v = s[j][e] * scale_log2;
-          if (bias) v = fmaf(__ldg(bias + (size_t)__ldg(bucket + min(max(qpos[r] - kp, 0), far)) * nh + head[r]), 1.4426950408889634f, v);
+          if (bias) v = fmaf(__ldg(bias + (size_t)head[r] * (far + 1) + min(max(qpos[r] - kp, 0), far)), 1.4426950408889634f, v);
         }
         s[j][e] = v;
         mx[r] = fmaxf(mx[r], v);
@@ -365,8 +381,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attn_mma_tile_kernel(const MmaPar
       const int key0 = tile_key0(t);
       const bool need_mask = !rows_full || key0 + BN - 1 > all_hi || key0 < all_lo;
       if (extra)
-        softmax_step<BN / 8, D / 8, true>(s, o, m, l, lo, pos, key0, p.scale_log2, lane, need_mask, keep, p.bias, p.bias_bucket,
-                                          p.bias_far, p.nh, head, pos);
+        softmax_step<BN / 8, D / 8, true>(s, o, m, l, lo, pos, key0, p.scale_log2, lane, need_mask, keep, p.bias, p.bias_far, head, pos);
       else
         softmax_step<BN / 8, D / 8>(s, o, m, l, lo, pos, key0, p.scale_log2, lane, need_mask);
       pv_tile<D, BN / 16>(o, s, vs, 0, lane);
@@ -495,8 +510,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attn_mma_split_kernel(const MmaPa
       const int key0 = tile_key0(t) + warp * 16;
       const bool need_mask = key0 < first_seen || key0 + 15 > kv_hi - 1;
       if (extra)
-        softmax_step<2, D / 8, true>(s, o, m, l, lo, hi, key0, p.scale_log2, lane, need_mask, keep, p.bias, p.bias_bucket, p.bias_far,
-                                     p.nh, head, qpos);
+        softmax_step<2, D / 8, true>(s, o, m, l, lo, hi, key0, p.scale_log2, lane, need_mask, keep, p.bias, p.bias_far, head, qpos);
       else
         softmax_step<2, D / 8>(s, o, m, l, lo, hi, key0, p.scale_log2, lane, need_mask);
       pv_tile<D, 1>(o, s, vs, warp, lane);
@@ -636,9 +650,9 @@ static int run_mma(const void* q, void* out, const void* kcache, const void* vca
                    const int* qsl, const int* ctx_lens, int B, int max_q_len, int q_stride, int out_stride,
                    int bt_stride, int nh, int nkv, int d, int block_size, float scale, int window, int split_size,
                    int max_splits, int grid_splits, float* part_acc, float* part_ml, int* tickets, cudaStream_t st,
-                   int keep_first = 0, const float* bias = nullptr, const int* bias_bucket = nullptr, int bias_far = 0) {
+                   int keep_first = 0, const float* bias = nullptr, int bias_far = 0) {
   if (B <= 0 || max_q_len <= 0) return 0;
-  if (keep_first < 0 || (bias && (!bias_bucket || bias_far < 0))) return (int)cudaErrorInvalidValue;
+  if (keep_first < 0 || (bias && bias_far < 0)) return (int)cudaErrorInvalidValue;
   if ((d != 64 && d != 128) || nkv <= 0 || nh % nkv != 0 || block_size <= 0) return (int)cudaErrorInvalidValue;
   const int g = nh / nkv;
   if (g > BM || (unsigned)B > 65535u || (unsigned)nkv > 65535u) return (int)cudaErrorInvalidValue;
@@ -655,7 +669,7 @@ static int run_mma(const void* q, void* out, const void* kcache, const void* vca
   p.split_size = split_size; p.max_splits = max_splits;
   p.grid_splits = grid_splits > 0 && grid_splits < max_splits ? grid_splits : max_splits;
   p.scale_log2 = scale * 1.4426950408889634f;
-  p.keep_first = keep_first; p.bias = bias; p.bias_bucket = bias_bucket; p.bias_far = bias_far;
+  p.keep_first = keep_first; p.bias = bias; p.bias_far = bias_far;
   if (split_size > 0) {
     if (g > 16 || split_size % BN != 0 || max_splits <= 0 || max_splits > 1024 || !part_acc || !part_ml || max_q_len != 1)
       return (int)cudaErrorInvalidValue;
@@ -678,10 +692,9 @@ KVF_API int kvf_paged_attention_mma_biased_bf16(const void* q, void* out, const 
                                                 const int* block_tables, const int* qsl, const int* ctx_lens, int B,
                                                 int max_q_len, int q_stride, int out_stride, int bt_stride, int nh,
                                                 int nkv, int d, int block_size, float scale, int window, int keep_first,
-                                                const float* bias, const int* bias_bucket, int bias_far, cudaStream_t st) {
+                                                const float* bias, int bias_far, cudaStream_t st) {
   return run_mma(q, out, kcache, vcache, block_tables, qsl, ctx_lens, B, max_q_len, q_stride, out_stride, bt_stride, nh,
-                 nkv, d, block_size, scale, window, 0, 0, 0, nullptr, nullptr, nullptr, st, keep_first, bias, bias_bucket,
-                 bias_far);
+                 nkv, d, block_size, scale, window, 0, 0, 0, nullptr, nullptr, nullptr, st, keep_first, bias, bias_far);
 }
 
 // The split form in one launch (see below) with kept first keys and a bias by distance.
@@ -690,8 +703,8 @@ KVF_API int kvf_paged_attention_decode_biased_bf16(const void* q, void* out, con
                                                    int q_stride, int out_stride, int bt_stride, int nh, int nkv, int d,
                                                    int block_size, float scale, int window, int split_size,
                                                    int max_splits, int grid_splits, float* part_acc, float* part_ml,
-                                                   int* tickets, int keep_first, const float* bias, const int* bias_bucket,
-                                                   int bias_far, cudaStream_t st);
+                                                   int* tickets, int keep_first, const float* bias, int bias_far,
+                                                   cudaStream_t st);
 
 // The split form in one launch: `tickets` holds B * nkv counters that are zero before the first
 // launch (each launch leaves them zero); the CTA that finishes last among the ranges of a
@@ -712,10 +725,10 @@ KVF_API int kvf_paged_attention_decode_biased_bf16(const void* q, void* out, con
                                                    int q_stride, int out_stride, int bt_stride, int nh, int nkv, int d,
                                                    int block_size, float scale, int window, int split_size,
                                                    int max_splits, int grid_splits, float* part_acc, float* part_ml,
-                                                   int* tickets, int keep_first, const float* bias, const int* bias_bucket,
-                                                   int bias_far, cudaStream_t st) {
+                                                   int* tickets, int keep_first, const float* bias, int bias_far,
+                                                   cudaStream_t st) {
   if (!tickets || split_size <= 0) return (int)cudaErrorInvalidValue;
   return run_mma(q, out, kcache, vcache, block_tables, qsl, ctx_lens, B, 1, q_stride, out_stride, bt_stride, nh, nkv, d,
                  block_size, scale, window, split_size, max_splits, grid_splits, part_acc, part_ml, tickets, st, keep_first, bias,
-                 bias_bucket, bias_far);
+                 bias_far);
 }

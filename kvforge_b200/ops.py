@@ -24,11 +24,11 @@ _SIGNATURES = {
     "kvf_rope_cache_{s}": "ppilppppppiiiiiilpp",
     "kvf_silu_mul_{s}": "ppliip",
     "kvf_cast_from_float_{s}": "pplp",
-    "kvf_paged_attention_generic_{s}": "pppppppiiiiiiiiiifiiiippiippip",
+    "kvf_paged_attention_generic_{s}": "pppppppiiiiiiiiiifiiiippiipip",
     "kvf_paged_attention_mma_bf16": "pppppppiiiiiiiiifiiiippp",
-    "kvf_paged_attention_mma_biased_bf16": "pppppppiiiiiiiiifiippip",
+    "kvf_paged_attention_mma_biased_bf16": "pppppppiiiiiiiiifiipip",
     "kvf_latent_attention_bf16": "ppppppiiiiiiiiifiiiippp",
-    "kvf_paged_attention_decode_biased_bf16": "pppppppiiiiiiiifiiiipppippip",
+    "kvf_paged_attention_decode_biased_bf16": "pppppppiiiiiiiifiiiipppipip",
     "kvf_paged_attention_tcgen05_bf16": "pppppppiiiiiiiiilfipipp",
     "kvf_paged_attention_decode_fused_bf16": "pppppppiiiiiiiifiiiipppp",
     "kvf_paged_attention_decode_tma_bf16": "pppppppiiiiiiiilfiiiippppiip",
@@ -468,10 +468,17 @@ def check_head_dim(d: int, most: int = 256) -> None:
 class DistanceBias:
     """A learned bias on attention scores by distance: ``table`` float ``[rows, heads]`` and
     ``bucket`` int32 ``[far + 1]``, the row for every distance up to ``far`` (farther keys take the
-    row of ``far``)."""
+    row of ``far``).  The kernels read ``by_distance`` float ``[heads, far + 1]``, the table spread out
+    over the distances with a head's values side by side: one load a score, and neighbouring keys in
+    neighbouring words."""
 
     table: torch.Tensor
     bucket: torch.Tensor
+    by_distance: torch.Tensor | None = None
+
+    def __post_init__(self) -> None:
+        if self.by_distance is None:
+            self.by_distance = self.table[self.bucket.long()].t().contiguous()
 
 
 def mma_attention_supported(dtype: torch.dtype, nh: int, nkv: int, d: int, decode_form: bool) -> bool:
@@ -587,13 +594,16 @@ def paged_attention(
         raise ValueError("paged_attention: cache shapes must be [num_blocks, nkv, block_size, d] and [..., dv]")
     if special and 4 * (32 * (d + 4) + (0 if vcache is kcache else 32 * (dv + 4)) + 16 * d + 512) > 227 * 1024:
         raise ValueError(f"paged_attention: heads of {d} and {dv} do not fit the kernel's shared memory")
-    bias_args = (None, None, 0)
+    bias_args = (None, 0)
     if bias is not None:
         _need(bias.table, torch.float32, "bias table")
         _need(bias.bucket, torch.int32, "bias buckets")
         if bias.table.dim() != 2 or bias.table.shape[1] != nh or bias.bucket.numel() < 1:
             raise ValueError("paged_attention: the bias table must be [rows, heads]")
-        bias_args = (_ptr(bias.table), _ptr(bias.bucket), bias.bucket.numel() - 1)
+        _need(bias.by_distance, torch.float32, "bias by distance")
+        if tuple(bias.by_distance.shape) != (nh, bias.bucket.numel()):
+            raise ValueError("paged_attention: the bias by distance must be [heads, far + 1]")
+        bias_args = (_ptr(bias.by_distance), bias.bucket.numel() - 1)
     if keep_first < 0:
         raise ValueError("paged_attention: keep_first is a count of keys")
     if dv != d:
